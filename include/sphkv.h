@@ -1,0 +1,223 @@
+/*
+ * sphkv.h -- C ABI of libsphkv_b200.so
+ *
+ * B200 (sm_100a) kernels for the Spherical-KV hot path: the spherical encode that
+ * writes codebook-quantised, bit-packed KV pages, and angle-domain decode attention
+ * over those pages.  Every entry point takes plain device pointers, sizes and a CUDA
+ * stream handle (a cudaStream_t passed as void*; NULL = legacy default stream).
+ * Nothing here allocates device memory except where a function says so; all
+ * buffers are caller-owned.
+ *
+ * Return value of every int function: 0 on success, a negative SPHKV_E_* code for a
+ * rejected argument, or a positive cudaError_t value if a launch failed.
+ * sphkv_last_error() returns a human-readable string for the last failure on the
+ * calling thread.
+ *
+ * Each declaration cites the reference interface (file:line in the Spherical-KV
+ * source tree) that it replaces or extends.
+ */
+#ifndef SPHKV_H_
+#define SPHKV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPHKV_ABI_VERSION 1
+
+/* error codes */
+#define SPHKV_OK 0
+#define SPHKV_E_ARG (-1)      /* null pointer / bad size / unsupported shape        */
+#define SPHKV_E_DTYPE (-2)    /* unsupported dtype tag                               */
+#define SPHKV_E_ALIGN (-3)    /* pointer or offset alignment not satisfied           */
+#define SPHKV_E_SCRATCH (-4)  /* scratch buffer too small                            */
+#define SPHKV_E_LIMIT (-5)    /* size beyond a documented fixed maximum              */
+
+/* dtype tags */
+#define SPHKV_F32 0
+#define SPHKV_BF16 1
+#define SPHKV_F16 2
+
+/* radius storage formats inside a K page (page header byte 2) */
+#define SPHKV_RADIUS_I8 0  /* int8 code * scale_g / 127, the reference page format   */
+#define SPHKV_RADIUS_F16 1 /* IEEE half per (token, group); header scales still set  */
+
+#define SPHKV_MAX_TIER_SLOTS 4
+#define SPHKV_MAX_GQA 8 /* query heads per KV head handled by one kernel pass        */
+
+/* Geometry of the codebook tensor and of the tiers stored in it.  The codebook
+ * tensor has the layout of LayerPool.cb_flat (sphkv_lut.py:108-111):
+ * f32 [Hkv][n_slots][G_max][C_max][g_max], zero padded.  A "slot" is the tier rank
+ * of make_tier_idx_map (sphkv_lut.py:7-14). */
+typedef struct sphkv_tiers {
+  int32_t n_slots;
+  int32_t G_max, C_max, g_max;
+  int32_t g[SPHKV_MAX_TIER_SLOTS];       /* group size per slot: 16 or 32            */
+  int32_t bits[SPHKV_MAX_TIER_SLOTS];    /* b_theta per slot (1..6), C = 2^bits      */
+  int32_t tier_id[SPHKV_MAX_TIER_SLOTS]; /* value written to page header byte 0      */
+} sphkv_tiers;
+
+/* ---- RoPE table ----------------------------------------------------------------
+ * Builds the cos/sin table the decode kernel gathers per key position.  Values are
+ * cos/sin of the fp32 product float(pos) * inv_freq[i], the same arguments the HF
+ * rotary module produces for the reference's tables
+ * (spherical_kv_pipeline.py:1591-1610).  Layout: f32 [max_pos][dh] where a row holds,
+ * for each 16-frequency block s and lane quad j, {cos f0..f3, sin f0..f3} with
+ * f = 16 s + {2j, 2j+1, 2j+8, 2j+9}.  inv_freq: device f32 [dh/2]. */
+int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh, const float* inv_freq,
+                           void* stream);
+
+/* ---- Encode ----------------------------------------------------------------------
+ * Bulk spherical encode + page build.  Replaces _encode_keys_with_codebooks
+ * (spherical_kv_pipeline.py:1130-1144) + build_page (pagebuilder.py:8-33) +
+ * PageHeader.to_tensor (paging.py:20-31) + pack_bits (bitpacking.py:5-29) for whole
+ * page lists, and the V/position page writes of _build_per_head_pages
+ * (spherical_kv_pipeline.py:1146-1228).
+ *
+ * Work is described per bundle: 64 token slots = 64/page_size pages that share one
+ * (KV head, tier slot); page_size > 64 uses one page per bundle. */
+typedef struct sphkv_encode_params {
+  const void* k_src;        /* [rows][Hkv][dh], k_dtype; pre-RoPE keys                */
+  const void* v_src;        /* same indexing, v_src_dtype; may be NULL (skip V)       */
+  const int32_t* src_index; /* [P][page_size] source row per page slot, -1 = empty    */
+  const int32_t* bundles;   /* [n_bundles][4] physical page ids, -1 = unused          */
+  const int32_t* page_head; /* [P] KV head of each page (codebook selector)           */
+  const int32_t* page_slot; /* [P] tier slot of each page                             */
+  const int32_t* ptable;    /* [P][3] (page_off, theta_off, radius_off) byte offsets,
+                               pointer_table.py:10-21                                 */
+  const float* codebooks;   /* see sphkv_tiers                                        */
+  uint8_t* k_pages;         /* out: byte pool                                         */
+  void* v_pool;             /* out: [P][page_size][dh], v_pool_dtype (F16 or BF16)    */
+  int64_t k_row_stride;     /* elements between consecutive source rows               */
+  int64_t k_head_stride;    /* elements between consecutive heads of a row            */
+  int64_t v_row_stride, v_head_stride;
+  int32_t n_bundles, n_pages, page_size, dh, Hkv;
+  int32_t k_dtype, v_src_dtype, v_pool_dtype;
+  int32_t radius_fmt;
+  sphkv_tiers tiers;
+} sphkv_encode_params;
+
+int sphkv_encode_pages(const sphkv_encode_params* p, void* stream);
+
+/* ---- Decode ----------------------------------------------------------------------
+ * Angle-domain decode attention over bit-packed pages with in-kernel back-rotation
+ * by each key's RoPE position, batch, split-K and log-sum-exp merge.  Numerics follow
+ * SphericalKVPipeline._compressed_head_attention_batched
+ * (spherical_kv_pipeline.py:2136-2177, 2348, 2364-2367); the table layout extends
+ * LayerPool (sphkv_lut.py:77-103) with a batch dimension; the call supersedes
+ * sphkv_logit_launcher (fused_decode.cpp:3-8) and the undefined fused_decode_ragged
+ * (call sites spherical_kv_pipeline.py:1109-1125). */
+typedef struct sphkv_decode_params {
+  const void* q;              /* [B][Hq][dh] q_dtype, post-RoPE at the query position */
+  const uint8_t* k_pages;     /* byte pool                                            */
+  const int32_t* ptable;      /* [P][3]                                               */
+  const void* v_pool;         /* [P][page_size][dh] v_dtype (F16/BF16); slots past a
+                                 page's count must hold finite values (zero-filled)   */
+  const int32_t* positions;   /* [P][page_size] key positions, -1 = empty             */
+  const int32_t* block_table; /* [B*Hkv][max_blocks] physical page id, -1 = hole      */
+  const int32_t* bits_table;  /* [B*Hkv][max_blocks] tier slot of each block          */
+  const int32_t* num_blocks;  /* [B*Hkv] blocks in use per (batch row, KV head)       */
+  const float* codebooks;     /* see sphkv_tiers                                      */
+  const float* rope_table;    /* from sphkv_rope_table_build; NULL = no rotation      */
+  void* out;                  /* [B][Hq][dh] out_dtype; may be NULL with out_partial  */
+  float* out_partial;         /* optional [B][Hq][dh+2]: (max, sum, acc) un-normalised,
+                                 natural-log max, the triple of decode_kernel.cu:212-217
+                                 taken over the whole local context                   */
+  float* page_ml;             /* optional [B][Hq][max_blocks][2] per-block (max, sum),
+                                 natural-log domain, the side output read at
+                                 spherical_kv_pipeline.py:1690-1693; only written for
+                                 page_size == 16                                      */
+  float* logits_out;          /* optional [B][Hq][max_blocks*page_size] f32: the scaled
+                                 logit of every stored token (slot order of the block
+                                 table); slots without a token are left untouched       */
+  void* scratch;              /* sphkv_decode_scratch_bytes() bytes, 256-aligned      */
+  int64_t scratch_bytes;
+  int32_t* status;            /* optional device int, OR-ed with SPHKV_ST_* bits      */
+  int32_t B, Hq, Hkv, dh, page_size, max_blocks, n_pages, max_pos;
+  int32_t q_dtype, v_dtype, out_dtype, radius_fmt;
+  int32_t n_ctas;             /* 0 = one per SM of the current device                 */
+  float sm_scale;
+  sphkv_tiers tiers;
+} sphkv_decode_params;
+
+#define SPHKV_ST_BAD_POSITION 1 /* a key position was outside [0, max_pos)            */
+#define SPHKV_ST_BAD_BLOCK 2    /* a block-table entry was >= n_pages                 */
+#define SPHKV_ST_BAD_SLOT 4     /* a bits-table entry was outside [0, n_slots)        */
+
+int64_t sphkv_decode_scratch_bytes(int32_t B, int32_t Hkv, int32_t dh, int32_t n_ctas);
+int sphkv_decode_paged(const sphkv_decode_params* p, void* stream);
+
+/* Log-sum-exp combine of R partial sets, each f32 [n_rows][dh+2] = (max, sum, acc),
+ * natural-log max.  Same math as sphkv_reduce_kernel (decode_kernel.cu:221-246) with a
+ * plain division (no +1e-8); rows whose total sum is 0 produce zeros.  Used after the
+ * all-gather of per-GPU partials in split-KV decode.  parts: [R][n_rows][dh+2]. */
+int sphkv_merge_partials(const float* parts, int32_t R, int32_t n_rows, int32_t dh, void* out,
+                         int32_t out_dtype, void* stream);
+
+/* ---- Reference-signature operators over the LayerPool layout ----------------------
+ * Pools as built by LayerPool.__init__ (sphkv_lut.py:77-103): theta_codes, radius_codes
+ * u8 [P][page_size][G_max]; r_scales f32 [P][G_max]; v_pool f16 [P][page_size][dh];
+ * block_table, bits_table i32 [Hkv][max_blocks]; cb_flat f32
+ * [Hkv][num_tiers][G_max][cb_max][g_max]; single sequence, post-RoPE keys. */
+
+/* Replaces sphkv_logit_launcher (fused_decode.cpp:3-8; kernels decode_kernel.cu:108-246),
+ * argument for argument, plus the stream.  out f32 [Hq][dh]; partial_scratch f32
+ * [Hq][max_blocks][dh+2] receives the per-page (m, l, acc) that
+ * spherical_kv_pipeline.py:1690-1693 reads back.  ctx_lens and max_ctx are accepted and
+ * unused, as in the reference. */
+int sphkv_pool_decode(const float* q_all, const float* cb_flat, const int32_t* tier_G,
+                      const int32_t* tier_g, const uint8_t* theta_codes,
+                      const uint8_t* radius_codes, const float* r_scales, const void* v_pool,
+                      const int32_t* block_table, const int32_t* bits_table,
+                      const int32_t* ctx_lens, float* out, float* partial_scratch,
+                      int32_t num_q_heads, int32_t num_kv_heads, int32_t kv_groups,
+                      int32_t num_tiers, int32_t max_blocks, int32_t page_size, int32_t dh,
+                      int32_t G_max, int32_t cb_max, int32_t g_max, float sm_scale, int32_t max_ctx,
+                      void* stream);
+
+/* Replaces sphkv_encode_append_launcher (fused_decode.cpp:10-14; kernel
+ * decode_kernel.cu:10-84).  num_kv is k_post.size(0) of the reference call.  pids: i64. */
+int sphkv_pool_encode_append(const float* k_post, const float* v_new, const float* decode_cb,
+                             uint8_t* theta_codes, uint8_t* radius_codes, float* r_scales,
+                             void* v_pool, const int64_t* pids, int32_t slot, int32_t G, int32_t g,
+                             int32_t C, int32_t G_max, int32_t dh, int32_t page_size,
+                             int32_t is_new_page, int32_t num_kv, void* stream);
+
+/* Implements the launcher new_fused_decode.cpp:3-22 declares and the reference never
+ * defines: logits from a q.centroid table.  q_lut f32 [Hq][num_tiers][G_max][cb_size_max];
+ * logits_out f32 [Hq][max_blocks*page_size]; holes, slots past ctx_lens and exact-zero
+ * logits get -1e9. */
+int sphkv_qlut_logits(const float* q_lut, const uint8_t* theta_codes, const uint8_t* radius_codes,
+                      const float* r_scales, const int32_t* block_table, const int32_t* bits_table,
+                      const int32_t* ctx_lens, float* logits_out, int32_t num_q_heads,
+                      int32_t num_kv_heads, int32_t kv_groups, int32_t num_tiers,
+                      int32_t max_blocks, int32_t page_size, int32_t G_max, int32_t cb_size_max,
+                      float sm_scale, int32_t max_ctx, void* stream);
+
+/* Implements fused_decode_ragged, which the reference calls
+ * (spherical_kv_pipeline.py:1109-1125, 1866-1870, 1907-1910) and never defines: logits
+ * over bit-packed byte pages of one tier with per-token back-rotation from the caller's
+ * HF-layout cos/sin tables f32 [table_rows][dh].  codebooks f32 [num_kv*G][2^b_theta][g];
+ * logits_out f32 [Hq][n_pages*page_size]. */
+int sphkv_ragged_logits(const uint8_t* pages, const int32_t* ptable, const int32_t* head_ids,
+                        const int32_t* positions, const float* cos_tbl, const float* sin_tbl,
+                        const float* q, const float* codebooks, float* logits_out, int32_t grp,
+                        int32_t num_kv, int32_t dh, int32_t G, int32_t g, int32_t b_theta,
+                        int32_t page_size, int32_t n_pages, int32_t Hq, int32_t table_rows,
+                        int32_t radius_fmt, int32_t reserved, void* stream);
+
+/* ---- Library ---------------------------------------------------------------------*/
+int sphkv_abi_version(void);
+const char* sphkv_last_error(void);
+/* sizeof() of sphkv_tiers (0), sphkv_encode_params (1), sphkv_decode_params (2) as this
+ * library was compiled; foreign-language bindings compare it with their own layout. */
+int sphkv_struct_size(int which);
+/* Number of SMs of the current device (grid sizing), or a negative error. */
+int sphkv_sm_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPHKV_H_ */

@@ -1,0 +1,399 @@
+// Kernels behind the reference's existing operator signatures.
+//
+//   sphkv_pool_decode         fused_decode.sphkv_decode        (fused_decode.py:12-26)
+//   sphkv_pool_encode_append  fused_decode.sphkv_encode_append (fused_decode.py:28-35)
+//   sphkv_qlut_logits         new_fused_decode.sphkv_logits    (new_fused_decode.py:22-43)
+//   sphkv_ragged_logits       fused_decode.fused_decode_ragged (call sites only:
+//                             spherical_kv_pipeline.py:1109-1125, 1866-1870)
+//
+// They read the LayerPool layout (sphkv_lut.py:77-103): one byte per centroid index and
+// per radius code, post-RoPE keys, single sequence.  The arithmetic of
+// decode_kernel.cu:10-246 is kept (sentinel mask for zero logits, +1e-8 in the final
+// division, running-max radius scale with in-place re-quantisation); the work split is
+// new: one CTA serves all query heads of a KV head per page through a q.centroid look-up
+// table instead of staging a 64 KiB codebook per (query head, page).
+#include "common.cuh"
+
+namespace sphkv {
+
+constexpr int kPoolThreads = 128;
+
+// ---- pool decode: per (KV head, logical page) partial (m, l, acc) for each query head ----
+__global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
+    const float* __restrict__ q_all, const float* __restrict__ cb_flat,
+    const int* __restrict__ tier_G_arr, const int* __restrict__ tier_g_arr,
+    const uint8_t* __restrict__ theta_codes, const uint8_t* __restrict__ radius_codes,
+    const float* __restrict__ r_scales, const __half* __restrict__ v_pool,
+    const int* __restrict__ block_table, const int* __restrict__ bits_table,
+    float* __restrict__ partial_out, int num_q_heads, int kv_groups, int num_tiers, int max_blocks,
+    int page_size, int dh, int G_max, int cb_max, int g_max, float sm_scale) {
+  const int hkv = blockIdx.x, page_idx = blockIdx.y, tid = threadIdx.x;
+  const int hq0 = hkv * kv_groups;
+  const int phys = block_table[hkv * max_blocks + page_idx];
+  if (phys < 0) {
+    for (int h = 0; h < kv_groups; ++h) {
+      float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
+      if (tid == 0) { po[0] = -INFINITY; po[1] = 0.f; }
+      for (int d = tid; d < dh; d += blockDim.x) po[2 + d] = 0.f;
+    }
+    return;
+  }
+  const int tier_idx = bits_table[hkv * max_blocks + page_idx];
+  const int G = tier_G_arr[tier_idx], g = tier_g_arr[tier_idx];
+
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  float* sq = reinterpret_cast<float*>(smem_raw);   // [kv_groups][dh]
+  float* lut = sq + kv_groups * dh;                  // [kv_groups][G_max][cb_max]
+  float* slog = lut + kv_groups * G_max * cb_max;    // [kv_groups][page_size]
+  float* srs = slog + kv_groups * page_size;         // [G_max]
+
+  for (int i = tid; i < kv_groups * dh; i += blockDim.x) sq[i] = q_all[(int64_t)hq0 * dh + i];
+  if (tid < G_max) srs[tid] = r_scales[(int64_t)phys * G_max + tid];
+  __syncthreads();
+
+  // q . centroid table for this tier; same summation order as decode_kernel.cu:186-188
+  const float* cb_t = cb_flat + ((int64_t)hkv * num_tiers + tier_idx) * G_max * cb_max * g_max;
+  for (int i = tid; i < kv_groups * G * cb_max; i += blockDim.x) {
+    const int c = i % cb_max, gg = (i / cb_max) % G, h = i / (cb_max * G);
+    const float* qg = sq + h * dh + gg * g;
+    const float* cw = cb_t + ((int64_t)gg * cb_max + c) * g_max;
+    float dot = 0.f;
+    for (int d = 0; d < g; ++d) dot += qg[d] * cw[d];
+    lut[(h * G_max + gg) * cb_max + c] = dot;
+  }
+  __syncthreads();
+
+  // logits: thread = token, all query heads of the KV head
+  for (int t = tid; t < page_size; t += blockDim.x) {
+    const uint8_t* th = theta_codes + ((int64_t)phys * page_size + t) * G_max;
+    const uint8_t* rc = radius_codes + ((int64_t)phys * page_size + t) * G_max;
+    for (int h = 0; h < kv_groups; ++h) {
+      float logit_sum = 0.f;
+      for (int gg = 0; gg < G; ++gg) {
+        const float r_hat = srs[gg] * (float)rc[gg] / 255.0f;
+        logit_sum += r_hat * lut[(h * G_max + gg) * cb_max + th[gg]];
+      }
+      slog[h * page_size + t] = (logit_sum == 0.f) ? -1e9f : logit_sum * sm_scale;
+    }
+  }
+  __syncthreads();
+
+  // per head: softmax statistics over the page and V accumulation; warp = head
+  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < kv_groups; h += nwarps) {
+    const float* lg = slog + h * page_size;
+    float m = -INFINITY;
+    for (int t = lane; t < page_size; t += 32) m = fmaxf(m, lg[t]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+    for (int t = lane; t < page_size; t += 32) l += __expf(lg[t] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
+    if (lane == 0) { po[0] = m; po[1] = l; }
+    for (int d0 = 2 * lane; d0 < dh; d0 += 64) {
+      float a0 = 0.f, a1 = 0.f;
+      const __half* vp = v_pool + (int64_t)phys * page_size * dh + d0;
+      for (int t = 0; t < page_size; ++t) {
+        const float pt = __expf(lg[t] - m);
+        const __half2 v2 = *reinterpret_cast<const __half2*>(vp + (int64_t)t * dh);
+        a0 += pt * __low2float(v2);
+        a1 += pt * __high2float(v2);
+      }
+      po[2 + d0] = a0;
+      po[2 + d0 + 1] = a1;
+    }
+  }
+}
+
+// log-sum-exp merge of the page partials, decode_kernel.cu:221-246
+__global__ void pool_reduce_kernel(const float* __restrict__ partial_out, float* __restrict__ out,
+                                   int dh, int max_pages) {
+  const int hq = blockIdx.x;
+  for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+    float m_f = -INFINITY, l_f = 0.f, a_f = 0.f;
+    for (int pg = 0; pg < max_pages; ++pg) {
+      const float* pr = partial_out + ((int64_t)hq * max_pages + pg) * (dh + 2);
+      const float m_s = pr[0], l_s = pr[1];
+      if (m_s == -INFINITY && l_s == 0.f) continue;
+      const float m_new = fmaxf(m_f, m_s);
+      const float alpha = __expf(m_f - m_new), beta = __expf(m_s - m_new);
+      a_f = alpha * a_f + beta * pr[2 + d];
+      l_f = alpha * l_f + beta * l_s;
+      m_f = m_new;
+    }
+    out[(int64_t)hq * dh + d] = a_f / (l_f + 1e-8f);
+  }
+}
+
+// ---- encode + append of one token per KV head, decode_kernel.cu:10-84 -----------------------
+// grid = KV heads, block = 32 * G: warp = group, lanes split the centroids.
+__global__ void pool_encode_append_kernel(
+    const float* __restrict__ k_post, const float* __restrict__ v_new,
+    const float* __restrict__ decode_cb, uint8_t* __restrict__ theta_codes,
+    uint8_t* __restrict__ radius_codes, float* __restrict__ r_scales, __half* __restrict__ v_pool,
+    const int64_t* __restrict__ pids, int slot, int G, int g, int C, int G_max, int dh,
+    int page_size, int is_new_page) {
+  const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t pid = pids[h];
+  const int64_t v_base = (pid * page_size + slot) * dh;
+  const int64_t code_base = (pid * page_size + slot) * G_max;
+  for (int d = tid; d < dh; d += blockDim.x) v_pool[v_base + d] = __float2half(v_new[(int64_t)h * dh + d]);
+  if (warp >= G) return;
+  const int grp = warp;
+  const float* k_g = k_post + (int64_t)h * dh + grp * g;
+  float norm_sq = 0.f;
+  for (int d = 0; d < g; ++d) norm_sq += k_g[d] * k_g[d];
+  const float norm = sqrtf(norm_sq + 1e-16f);
+  const float inv_norm = 1.0f / (norm + 1e-8f);
+  const float* cb = decode_cb + ((int64_t)h * G * C + (int64_t)grp * C) * g;
+  float best_sim = -1e30f;
+  int best_code = 0;
+  for (int c = lane; c < C; c += 32) {  // ascending per lane: strict > keeps the lowest index
+    float sim = 0.f;
+    for (int d = 0; d < g; ++d) sim += k_g[d] * inv_norm * cb[(int64_t)c * g + d];
+    if (sim > best_sim) { best_sim = sim; best_code = c; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float os = __shfl_xor_sync(0xffffffffu, best_sim, o);
+    const int oc = __shfl_xor_sync(0xffffffffu, best_code, o);
+    if (os > best_sim || (os == best_sim && oc < best_code)) { best_sim = os; best_code = oc; }
+  }
+  float r_scale;
+  const float prev_scale = is_new_page ? 0.f : r_scales[pid * G_max + grp];
+  if (is_new_page || norm > prev_scale) {
+    if (!is_new_page) {
+      const float ratio = prev_scale / (norm + 1e-8f);
+      for (int t = lane; t < slot; t += 32) {
+        const int64_t idx = (pid * page_size + t) * G_max + grp;
+        float rescaled = (float)radius_codes[idx] * ratio;
+        rescaled = fminf(fmaxf(roundf(rescaled), 0.f), 255.f);
+        radius_codes[idx] = (uint8_t)rescaled;
+      }
+    }
+    r_scale = norm;
+  } else {
+    r_scale = prev_scale;
+  }
+  if (lane == 0) {
+    theta_codes[code_base + grp] = (uint8_t)best_code;
+    if (is_new_page || norm > prev_scale) r_scales[pid * G_max + grp] = norm;
+    float r_q = roundf(norm / (r_scale + 1e-8f) * 255.0f);
+    r_q = fminf(fmaxf(r_q, 0.f), 255.f);
+    radius_codes[code_base + grp] = (uint8_t)r_q;
+  }
+}
+
+// ---- logits from a precomputed q.centroid table (new_fused_decode.cpp:3-22) ------------------
+// q_lut f32 [Hq][num_tiers][G_max][cb_size_max]; logits_out f32 [Hq][max_blocks*page_size].
+// Holes, slots past ctx_lens and exact-zero logits get the -1e9 sentinel of
+// decode_kernel.cu:194.  Tier geometry comes from the table itself: groups >= G of a tier
+// have zero radius codes in the pool and contribute nothing.
+__global__ void qlut_logits_kernel(const float* __restrict__ q_lut,
+                                   const uint8_t* __restrict__ theta_codes,
+                                   const uint8_t* __restrict__ radius_codes,
+                                   const float* __restrict__ r_scales,
+                                   const int* __restrict__ block_table,
+                                   const int* __restrict__ bits_table,
+                                   const int* __restrict__ ctx_lens, float* __restrict__ logits_out,
+                                   int num_q_heads, int kv_groups, int num_tiers, int max_blocks,
+                                   int page_size, int G_max, int cb_size_max, float sm_scale) {
+  const int hkv = blockIdx.x, page_idx = blockIdx.y;
+  const int phys = block_table[hkv * max_blocks + page_idx];
+  const int tier_idx = phys >= 0 ? bits_table[hkv * max_blocks + page_idx] : 0;
+  const int ctx = ctx_lens ? ctx_lens[hkv] : max_blocks * page_size;
+  for (int i = threadIdx.x; i < kv_groups * page_size; i += blockDim.x) {
+    const int h = i / page_size, t = i - h * page_size;
+    const int hq = hkv * kv_groups + h;
+    float outv = -1e9f;
+    if (phys >= 0 && page_idx * page_size + t < ctx) {
+      const uint8_t* th = theta_codes + ((int64_t)phys * page_size + t) * G_max;
+      const uint8_t* rc = radius_codes + ((int64_t)phys * page_size + t) * G_max;
+      const float* lut = q_lut + ((int64_t)hq * num_tiers + tier_idx) * G_max * cb_size_max;
+      float s = 0.f;
+      for (int gg = 0; gg < G_max; ++gg) {
+        const float r_hat = r_scales[(int64_t)phys * G_max + gg] * (float)rc[gg] / 255.0f;
+        s += r_hat * lut[gg * cb_size_max + th[gg]];
+      }
+      if (s != 0.f) outv = s * sm_scale;
+    }
+    logits_out[(int64_t)hq * max_blocks * page_size + (int64_t)page_idx * page_size + t] = outv;
+  }
+}
+
+// ---- logits over bit-packed byte pages with per-token back-rotation --------------------------
+// Restates spherical_kv_pipeline.py:2143-2176 per (token, query head): rotate q by the key
+// position with the caller's HF-layout tables, normalise per group, clamp the cosine,
+// weight by the de-quantised radius.  Output [Hq][n_pages * page_size]; slots with
+// position < 0 or past the page count, and heads outside the page's KV head, get 0.
+__global__ void ragged_logits_kernel(const uint8_t* __restrict__ pages,
+                                     const int* __restrict__ ptable,
+                                     const int* __restrict__ head_ids,
+                                     const int* __restrict__ positions,
+                                     const float* __restrict__ cos_tbl,
+                                     const float* __restrict__ sin_tbl, const float* __restrict__ q,
+                                     const float* __restrict__ codebooks,
+                                     float* __restrict__ logits_out, int grp, int num_kv, int dh,
+                                     int G, int g, int b_theta, int page_size, int n_pages, int Hq,
+                                     int table_rows, int radius_fmt) {
+  const int pg = blockIdx.x;
+  const int hkv = head_ids[pg];
+  const int poff = ptable[3 * pg], toff = ptable[3 * pg + 1], roff = ptable[3 * pg + 2];
+  const int count = pages[poff + 1];
+  const int C = 1 << b_theta, half = dh >> 1;
+  const float inv_sqrt = rsqrtf((float)dh);
+  const int64_t out_stride = (int64_t)n_pages * page_size;
+  for (int i = threadIdx.x; i < Hq * page_size; i += blockDim.x) {
+    const int hq = i / page_size, t = i - hq * page_size;
+    float outv = 0.f;
+    const int pos = positions[(int64_t)pg * page_size + t];
+    if (hq / grp == hkv && hkv < num_kv && t < count && pos >= 0 && pos < table_rows) {
+      const float* qh = q + (int64_t)hq * dh;
+      const float* cr = cos_tbl + (int64_t)pos * dh;
+      const float* sr = sin_tbl + (int64_t)pos * dh;
+      for (int gg = 0; gg < G; ++gg) {
+        const int64_t bit = ((int64_t)t * G + gg) * b_theta;
+        uint32_t w = 0;
+        for (int bb = 0; bb < 2; ++bb) w |= (uint32_t)pages[toff + (bit >> 3) + bb] << (8 * bb);
+        const int code = (int)((w >> (bit & 7)) & (uint32_t)(C - 1));
+        float rad;
+        if (radius_fmt == SPHKV_RADIUS_F16) {
+          const uint16_t hv = (uint16_t)pages[roff + 2 * (t * G + gg)] |
+                              ((uint16_t)pages[roff + 2 * (t * G + gg) + 1] << 8);
+          rad = __half2float(__ushort_as_half(hv));
+        } else {
+          float sc;
+          memcpy(&sc, pages + poff + 8 + 4 * gg, 4);
+          rad = sc * (float)(int8_t)pages[roff + t * G + gg] / 127.0f;
+        }
+        const float* cw = codebooks + ((int64_t)(hkv * G + gg) * C + code) * g;
+        float nsq = 0.f, dot = 0.f;
+        for (int d = 0; d < g; ++d) {
+          const int dd = gg * g + d;
+          const float rh = dd < half ? -qh[dd + half] : qh[dd - half];
+          const float qr = qh[dd] * cr[dd] - rh * sr[dd];
+          nsq += qr * qr;
+          dot += qr * cw[d];
+        }
+        const float qn = fmaxf(sqrtf(nsq), 1e-6f);
+        const float cpg = fminf(fmaxf(dot / qn, -1.f), 1.f);
+        outv += qn * cpg * rad;
+      }
+      outv *= inv_sqrt;
+    }
+    logits_out[(int64_t)hq * out_stride + (int64_t)pg * page_size + t] = outv;
+  }
+}
+
+}  // namespace sphkv
+
+using namespace sphkv;
+
+extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const int32_t* tier_G,
+                                 const int32_t* tier_g, const uint8_t* theta_codes,
+                                 const uint8_t* radius_codes, const float* r_scales,
+                                 const void* v_pool, const int32_t* block_table,
+                                 const int32_t* bits_table, const int32_t* ctx_lens, float* out,
+                                 float* partial_scratch, int32_t num_q_heads, int32_t num_kv_heads,
+                                 int32_t kv_groups, int32_t num_tiers, int32_t max_blocks,
+                                 int32_t page_size, int32_t dh, int32_t G_max, int32_t cb_max,
+                                 int32_t g_max, float sm_scale, int32_t max_ctx, void* stream) {
+  (void)ctx_lens;  // validity is encoded by block_table == -1 and the zero-logit sentinel,
+  (void)max_ctx;   // as in decode_kernel.cu:120,139-144,194
+  SPHKV_REQUIRE(q_all && cb_flat && tier_G && tier_g && theta_codes && radius_codes && r_scales &&
+                    v_pool && block_table && bits_table && out && partial_scratch,
+                SPHKV_E_ARG, "pool_decode: NULL pointer");
+  SPHKV_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && kv_groups > 0 &&
+                    num_q_heads == num_kv_heads * kv_groups,
+                SPHKV_E_ARG, "pool_decode: Hq=%d Hkv=%d groups=%d", num_q_heads, num_kv_heads,
+                kv_groups);
+  SPHKV_REQUIRE(max_blocks > 0 && page_size > 0 && dh > 0 && (dh & 1) == 0 && G_max > 0 &&
+                    cb_max > 0 && g_max > 0 && num_tiers > 0,
+                SPHKV_E_ARG, "pool_decode: bad size");
+  const size_t smem = ((size_t)kv_groups * dh + (size_t)kv_groups * G_max * cb_max +
+                       (size_t)kv_groups * page_size + G_max) * sizeof(float);
+  SPHKV_REQUIRE(smem <= 200 * 1024, SPHKV_E_LIMIT, "pool_decode: needs %zu B shared memory", smem);
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(pool_page_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      set_error("pool_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = smem;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  pool_page_kernel<<<dim3(num_kv_heads, max_blocks), kPoolThreads, smem, st>>>(
+      q_all, cb_flat, tier_G, tier_g, theta_codes, radius_codes, r_scales,
+      reinterpret_cast<const __half*>(v_pool), block_table, bits_table, partial_scratch,
+      num_q_heads, kv_groups, num_tiers, max_blocks, page_size, dh, G_max, cb_max, g_max, sm_scale);
+  if (int rc = check_launch("pool_page_kernel")) return rc;
+  pool_reduce_kernel<<<num_q_heads, 128, 0, st>>>(partial_scratch, out, dh, max_blocks);
+  return check_launch("pool_reduce_kernel");
+}
+
+extern "C" int sphkv_pool_encode_append(const float* k_post, const float* v_new,
+                                        const float* decode_cb, uint8_t* theta_codes,
+                                        uint8_t* radius_codes, float* r_scales, void* v_pool,
+                                        const int64_t* pids, int32_t slot, int32_t G, int32_t g,
+                                        int32_t C, int32_t G_max, int32_t dh, int32_t page_size,
+                                        int32_t is_new_page, int32_t num_kv, void* stream) {
+  SPHKV_REQUIRE(k_post && v_new && decode_cb && theta_codes && radius_codes && r_scales && v_pool &&
+                    pids,
+                SPHKV_E_ARG, "encode_append: NULL pointer");
+  SPHKV_REQUIRE(num_kv > 0 && G > 0 && G <= 32 && g > 0 && C > 0 && G <= G_max && G * g <= dh &&
+                    slot >= 0 && slot < page_size,
+                SPHKV_E_ARG, "encode_append: G=%d g=%d C=%d G_max=%d dh=%d slot=%d page_size=%d", G,
+                g, C, G_max, dh, slot, page_size);
+  pool_encode_append_kernel<<<num_kv, 32 * G, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      k_post, v_new, decode_cb, theta_codes, radius_codes, r_scales,
+      reinterpret_cast<__half*>(v_pool), pids, slot, G, g, C, G_max, dh, page_size, is_new_page);
+  return check_launch("pool_encode_append_kernel");
+}
+
+extern "C" int sphkv_qlut_logits(const float* q_lut, const uint8_t* theta_codes,
+                                 const uint8_t* radius_codes, const float* r_scales,
+                                 const int32_t* block_table, const int32_t* bits_table,
+                                 const int32_t* ctx_lens, float* logits_out, int32_t num_q_heads,
+                                 int32_t num_kv_heads, int32_t kv_groups, int32_t num_tiers,
+                                 int32_t max_blocks, int32_t page_size, int32_t G_max,
+                                 int32_t cb_size_max, float sm_scale, int32_t max_ctx,
+                                 void* stream) {
+  (void)max_ctx;
+  SPHKV_REQUIRE(q_lut && theta_codes && radius_codes && r_scales && block_table && bits_table &&
+                    logits_out,
+                SPHKV_E_ARG, "qlut_logits: NULL pointer");
+  SPHKV_REQUIRE(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads == num_kv_heads * kv_groups &&
+                    max_blocks > 0 && page_size > 0 && G_max > 0 && cb_size_max > 0 && num_tiers > 0,
+                SPHKV_E_ARG, "qlut_logits: bad size");
+  qlut_logits_kernel<<<dim3(num_kv_heads, max_blocks), 128, 0,
+                       reinterpret_cast<cudaStream_t>(stream)>>>(
+      q_lut, theta_codes, radius_codes, r_scales, block_table, bits_table, ctx_lens, logits_out,
+      num_q_heads, kv_groups, num_tiers, max_blocks, page_size, G_max, cb_size_max, sm_scale);
+  return check_launch("qlut_logits_kernel");
+}
+
+extern "C" int sphkv_ragged_logits(const uint8_t* pages, const int32_t* ptable,
+                                   const int32_t* head_ids, const int32_t* positions,
+                                   const float* cos_tbl, const float* sin_tbl, const float* q,
+                                   const float* codebooks, float* logits_out, int32_t grp,
+                                   int32_t num_kv, int32_t dh, int32_t G, int32_t g, int32_t b_theta,
+                                   int32_t page_size, int32_t n_pages, int32_t Hq,
+                                   int32_t table_rows, int32_t radius_fmt, int32_t reserved,
+                                   void* stream) {
+  (void)reserved;
+  SPHKV_REQUIRE(pages && ptable && head_ids && positions && cos_tbl && sin_tbl && q && codebooks &&
+                    logits_out,
+                SPHKV_E_ARG, "ragged_logits: NULL pointer");
+  SPHKV_REQUIRE(n_pages > 0 && grp > 0 && num_kv > 0 && Hq == grp * num_kv && G * g == dh &&
+                    (dh & 1) == 0 && b_theta >= 1 && b_theta <= 8 && page_size > 0 && table_rows > 0,
+                SPHKV_E_ARG, "ragged_logits: bad size (Hq=%d grp=%d num_kv=%d G=%d g=%d dh=%d)", Hq,
+                grp, num_kv, G, g, dh);
+  ragged_logits_kernel<<<n_pages, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pages, ptable, head_ids, positions, cos_tbl, sin_tbl, q, codebooks, logits_out, grp, num_kv,
+      dh, G, g, b_theta, page_size, n_pages, Hq, table_rows, radius_fmt);
+  return check_launch("ragged_logits_kernel");
+}

@@ -1,0 +1,158 @@
+"""torch-facing wrappers over the C ABI: device pointers in, kernels launched on the
+current CUDA stream.  torch is used for memory, streams and dtype bookkeeping only.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from .pages import PagedCache, PageLists, TierSet, build_page_lists
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise _lib.SphKVError("expected contiguous CUDA tensors")
+
+
+def hf_inv_freq(dh: int, base: float = 500000.0) -> torch.Tensor:
+    """inv_freq exactly as the HF rotary module computes it (default rope type):
+    1 / base ** (arange(0, dh, 2) / dh) in fp32 on the CPU."""
+    return 1.0 / (base ** (torch.arange(0, dh, 2, dtype=torch.int64).float() / dh))
+
+
+def rope_table(max_pos: int, dh: int, base: float = 500000.0, device="cuda",
+               inv_freq: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """cos/sin table in the decode kernel's lane layout, f32 [max_pos, dh]."""
+    lib = _lib.load()
+    if inv_freq is None:
+        inv_freq = hf_inv_freq(dh, base)
+    inv = inv_freq.to(device=device, dtype=torch.float32).contiguous()
+    assert inv.numel() == dh // 2
+    table = torch.empty(max_pos, dh, dtype=torch.float32, device=device)
+    _lib.check(lib.sphkv_rope_table_build(table.data_ptr(), max_pos, dh, inv.data_ptr(), _stream()),
+               "sphkv_rope_table_build")
+    return table
+
+
+def encode_pages(k_src: torch.Tensor, v_src: Optional[torch.Tensor], lists: PageLists,
+                 codebooks: torch.Tensor, tiers: TierSet, radius_fmt: int = _lib.RADIUS_I8,
+                 v_dtype: torch.dtype = torch.float16,
+                 out: Optional[PagedCache] = None) -> PagedCache:
+    """Encodes [rows, Hkv, dh] pre-RoPE keys (and values) into the pages `lists` describes.
+
+    Mirrors _encode_keys_with_codebooks + build_page_from_codes over whole page lists
+    (spherical_kv_pipeline.py:1130-1144, 1162-1213).  Returns the PagedCache (re-using the
+    pools of `out` when given).
+    """
+    lib = _lib.load()
+    _need_cuda(k_src, v_src, codebooks, lists.src_index, lists.bundles, lists.ptable)
+    rows, hkv, dh = k_src.shape
+    assert dh == tiers.dh and hkv == lists.Hkv
+    dev = k_src.device
+    if out is None:
+        k_pages = torch.zeros(lists.pool_bytes, dtype=torch.uint8, device=dev)
+        v_pool = torch.zeros(lists.n_pages, lists.page_size, dh, dtype=v_dtype, device=dev)
+        out = PagedCache(tiers=tiers, lists=lists, codebooks=codebooks, k_pages=k_pages,
+                         v_pool=v_pool, radius_fmt=radius_fmt)
+    p = _lib.EncodeParams()
+    p.k_src, p.v_src = k_src.data_ptr(), _ptr(v_src)
+    p.src_index, p.bundles = lists.src_index.data_ptr(), lists.bundles.data_ptr()
+    p.page_head, p.page_slot = lists.page_head.data_ptr(), lists.page_slot.data_ptr()
+    p.ptable, p.codebooks = lists.ptable.data_ptr(), codebooks.data_ptr()
+    p.k_pages, p.v_pool = out.k_pages.data_ptr(), out.v_pool.data_ptr()
+    p.k_row_stride, p.k_head_stride = k_src.stride(0), k_src.stride(1)
+    if v_src is not None:
+        p.v_row_stride, p.v_head_stride = v_src.stride(0), v_src.stride(1)
+        p.v_src_dtype = _DT[v_src.dtype]
+    p.n_bundles, p.n_pages = lists.bundles.shape[0], lists.n_pages
+    p.page_size, p.dh, p.Hkv = lists.page_size, dh, hkv
+    p.k_dtype, p.v_pool_dtype = _DT[k_src.dtype], _DT[out.v_pool.dtype]
+    p.radius_fmt = radius_fmt
+    p.tiers = tiers.to_c()
+    _lib.check(lib.sphkv_encode_pages(C.byref(p), _stream()), "sphkv_encode_pages")
+    return out
+
+
+def decode_scratch(cache: PagedCache, n_ctas: int = 0) -> torch.Tensor:
+    lib = _lib.load()
+    L = cache.lists
+    nbytes = lib.sphkv_decode_scratch_bytes(L.B, L.Hkv, cache.dh, n_ctas)
+    if nbytes <= 0:
+        raise _lib.SphKVError("sphkv_decode_scratch_bytes rejected the shape")
+    return torch.empty(nbytes, dtype=torch.uint8, device=cache.k_pages.device)
+
+
+def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor],
+                 sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, out_partial: Optional[torch.Tensor] = None,
+                 page_ml: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
+                 n_ctas: int = 0,
+                 want_out: bool = True) -> torch.Tensor:
+    """One decode-attention step over the compressed cache.
+
+    q: [B, Hq, dh] post-RoPE at the query position.  rope: table from rope_table() (None =
+    keys are stored post-RoPE, no rotation).  Returns out [B, Hq, dh]; with `out_partial`
+    ([B, Hq, dh+2] f32) the un-normalised (max, sum, acc) triple is written too.
+    Numerics: spherical_kv_pipeline.py:2136-2177 with sm_scale = 1/sqrt(dh).
+    """
+    lib = _lib.load()
+    L = cache.lists
+    B, Hq, dh = q.shape
+    _need_cuda(q, out, out_partial, page_ml, logits_out, rope)
+    assert B == L.B and dh == cache.dh
+    if cache.scratch is None:
+        cache.scratch = decode_scratch(cache, n_ctas)
+    if cache.status is None:
+        cache.status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    if out is None and want_out:
+        out = torch.empty(B, Hq, dh, dtype=out_dtype or q.dtype, device=q.device)
+    p = _lib.DecodeParams()
+    p.q, p.k_pages, p.ptable = q.data_ptr(), cache.k_pages.data_ptr(), L.ptable.data_ptr()
+    p.v_pool, p.positions = cache.v_pool.data_ptr(), L.positions.data_ptr()
+    p.block_table, p.bits_table = L.block_table.data_ptr(), L.bits_table.data_ptr()
+    p.num_blocks, p.codebooks = L.num_blocks.data_ptr(), cache.codebooks.data_ptr()
+    p.rope_table = _ptr(rope)
+    p.out, p.out_partial, p.page_ml = _ptr(out), _ptr(out_partial), _ptr(page_ml)
+    p.logits_out = _ptr(logits_out)
+    p.scratch, p.scratch_bytes = cache.scratch.data_ptr(), cache.scratch.numel()
+    p.status = cache.status.data_ptr()
+    p.B, p.Hq, p.Hkv, p.dh = B, Hq, L.Hkv, dh
+    p.page_size, p.max_blocks, p.n_pages = L.page_size, L.max_blocks, L.n_pages
+    p.max_pos = 0 if rope is None else rope.shape[0]
+    p.q_dtype, p.v_dtype = _DT[q.dtype], _DT[cache.v_pool.dtype]
+    p.out_dtype = _DT[out.dtype] if out is not None else _lib.F32
+    p.radius_fmt, p.n_ctas = cache.radius_fmt, n_ctas
+    p.sm_scale = (1.0 / math.sqrt(dh)) if sm_scale is None else sm_scale
+    p.tiers = cache.tiers.to_c()
+    _lib.check(lib.sphkv_decode_paged(C.byref(p), _stream()), "sphkv_decode_paged")
+    return out
+
+
+def merge_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """parts f32 [R, n_rows, dh+2] -> [n_rows, dh]; log-sum-exp combine
+    (decode_kernel.cu:221-246 without the +1e-8)."""
+    lib = _lib.load()
+    _need_cuda(parts, out)
+    R, n_rows, w = parts.shape
+    dh = w - 2
+    if out is None:
+        out = torch.empty(n_rows, dh, dtype=out_dtype, device=parts.device)
+    _lib.check(lib.sphkv_merge_partials(parts.data_ptr(), R, n_rows, dh, out.data_ptr(),
+                                        _DT[out.dtype], _stream()), "sphkv_merge_partials")
+    return out

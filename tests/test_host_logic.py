@@ -1,0 +1,127 @@
+"""CPU: host-side page-list construction, the C-ABI surface, argument validation."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from util import ROOT, load_oracle, load_pkg
+
+pkg = load_pkg()
+orc = load_oracle()
+synth = pkg.synth
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "sphkv.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = set(re.findall(r"\b(sphkv_[a-z_0-9]+)\s*\(", hdr))
+    assert {"sphkv_encode_pages", "sphkv_decode_paged", "sphkv_pool_decode",
+            "sphkv_pool_encode_append", "sphkv_qlut_logits", "sphkv_ragged_logits",
+            "sphkv_merge_partials", "sphkv_rope_table_build"} <= declared
+    lib = ctypes.CDLL(pkg._lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert declared == set(pkg._lib.SIGNATURES), declared ^ set(pkg._lib.SIGNATURES)
+    assert pkg._lib.load().sphkv_abi_version() == 1
+
+
+def test_struct_sizes_match_header_layout():
+    lib = pkg._lib.load()  # load() itself raises on a layout mismatch
+    assert ctypes.sizeof(pkg._lib.Tiers) == 16 * 4 == lib.sphkv_struct_size(0)
+    assert ctypes.sizeof(pkg._lib.EncodeParams) == lib.sphkv_struct_size(1)
+    assert ctypes.sizeof(pkg._lib.DecodeParams) == lib.sphkv_struct_size(2)
+    assert lib.sphkv_struct_size(3) == -1
+
+
+def test_argument_validation_without_gpu():
+    lib = pkg._lib.load()
+    p = pkg._lib.DecodeParams()
+    assert lib.sphkv_decode_paged(ctypes.byref(p), None) == -1
+    assert b"NULL" in lib.sphkv_last_error()
+    assert lib.sphkv_merge_partials(None, 1, 1, 1, None, 0, None) == -1
+    assert lib.sphkv_decode_scratch_bytes(0, 8, 128, 148) < 0
+    assert lib.sphkv_decode_scratch_bytes(8, 8, 128, 148) == 512 + (148 + 64) * 8 * 130 * 4
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(pkg._lib, "_lib", None)
+    monkeypatch.setattr(pkg._lib, "LIB_PATH", "/nonexistent/libsphkv_b200.so")
+    with pytest.raises(pkg.SphKVError, match="no CPU or PyTorch fallback"):
+        pkg._lib.load()
+
+
+@pytest.mark.parametrize("page_size", [16, 32, 128])
+@pytest.mark.parametrize("shuffle", [None, 3])
+def test_page_lists_partition_tokens(page_size, shuffle):
+    B, Hkv, T, dh = 2, 3, 333, 128
+    tiers = pkg.TierSet(dh, pkg.REFERENCE_TIERS)
+    assign = synth.make_tier_assign(B, Hkv, T, {1: 0.3, 2: 0.4, 3: 0.1}, seed=9, per_head=True)
+    L = pkg.build_page_lists(assign, tiers, page_size, shuffle_seed=shuffle)
+    N = page_size
+    # every retained token appears exactly once, in the page of its (unit, tier)
+    seen = torch.zeros(B, Hkv, T, dtype=torch.int32)
+    for u in range(B * Hkv):
+        b, h = divmod(u, Hkv)
+        nb = int(L.num_blocks[u])
+        assert (L.block_table[u, nb:] == -1).all() and (L.block_table[u, :nb] >= 0).all()
+        last_slot, last_pos = -1, -1
+        for lb in range(nb):
+            ph = int(L.block_table[u, lb])
+            s = int(L.bits_table[u, lb])
+            assert int(L.page_head[ph]) == h and int(L.page_slot[ph]) == s
+            c = int(L.page_count[ph])
+            pos = L.positions[ph]
+            assert (pos[:c] >= 0).all() and (pos[c:] == -1).all() and 1 <= c <= N
+            assert torch.equal(L.src_index[ph, :c], pos[:c] + b * T)
+            assert (assign[b, h, pos[:c].long()] == tiers.tiers[s].tier_id).all()
+            if s != last_slot:
+                assert s > last_slot
+                last_slot, last_pos = s, -1
+            assert (pos[:c].diff() > 0).all() and int(pos[0]) > last_pos
+            last_pos = int(pos[c - 1])
+            seen[b, h, pos[:c].long()] += 1
+    assert torch.equal(seen, (assign != 0).int())
+    # pointer table: pages do not overlap, offsets follow the reference arithmetic
+    pt = L.ptable.long()
+    order = torch.argsort(pt[:, 0])
+    for i, ph in enumerate(order.tolist()):
+        s = int(L.page_slot[ph]); t = tiers.tiers[s]; G = dh // t.g; c = int(L.page_count[ph])
+        assert pt[ph, 0] % 16 == 0
+        assert pt[ph, 1] == pt[ph, 0] + 8 + 4 * G
+        assert pt[ph, 2] == pt[ph, 1] + (c * G * t.b_theta + 7) // 8
+        end = pt[ph, 2] + c * G
+        nxt = pt[order[i + 1], 0] if i + 1 < len(order) else L.pool_bytes
+        assert end <= nxt
+    # bundles: each page once, homogeneous (head, slot)
+    bun = L.bundles
+    ids = bun[bun >= 0]
+    assert sorted(ids.tolist()) == list(range(L.n_pages))
+    ppb = 1 if N >= 64 else 64 // N
+    assert (bun[:, ppb:] == -1).all()
+    for row in bun.tolist():
+        live = [x for x in row if x >= 0]
+        assert len({(int(L.page_head[x]), int(L.page_slot[x])) for x in live}) == 1
+
+
+def test_budget_fractions():
+    f = synth.budget_fractions(96)
+    assert abs(f[1] - 0.3097) < 1e-3 and abs(f[2] - 0.6194) < 1e-3
+    assert synth.budget_fractions(160) == {1: 1.0}
+    f = synth.budget_fractions(48)
+    assert abs(f[1] + f[2] - 48 / 103.3333) < 1e-4
+
+
+def test_tier_set_codebook_packing():
+    dh = 128
+    tiers = pkg.TierSet(dh, pkg.REFERENCE_TIERS)
+    cbs = synth.make_codebooks(2, dh, pkg.REFERENCE_TIERS, seed=1)
+    flat = tiers.pack_codebooks(cbs)
+    assert tuple(flat.shape) == (2, 3, 8, 64, 32)
+    assert torch.equal(flat[:, 0, :8, :64, :16], cbs[0]) and (flat[:, 0, :, :, 16:] == 0).all()
+    assert torch.equal(flat[:, 2, :4, :8, :32], cbs[2]) and (flat[:, 2, 4:] == 0).all()
+    c = tiers.to_c()
+    assert (c.n_slots, c.G_max, c.C_max, c.g_max) == (3, 8, 64, 32)
+    assert list(c.g)[:3] == [16, 16, 32] and list(c.bits)[:3] == [6, 4, 3]
