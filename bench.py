@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: compressed-KV decode attention, Llama-3.1-8B layer shape,
+32-layer sweep at context 32768, batch 8 (one "step" = one decode step of all 32 layers).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--budget 96] [--impl reference]
+
+Prints ONE JSON line (rank 0).  `value` = microseconds per layer-step with the cache
+resident in HBM (CUDA-graph replay of the 32 layer-steps); `e2e` = the same through the
+public API with the step's queries copied from pinned host memory and the outputs read back
+inside the timed region.  Under torchrun every rank owns its own batch rows (units are
+independent: no data-path collective), so per-GPU work is fixed ("weak").
+
+`--impl reference` times the CPU restatement of the reference's torch path
+(oracle/oracle.py) on a bounded sample of the same workload with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+CFG = dict(B=8, Hq=32, Hkv=8, dh=128, ctx=32768, layers=32, page_size=16)
+METRIC, UNIT = "decode_attn_us_per_layer_step", "us"
+
+
+def algorithmic_bytes(lists, tiers, dh: int) -> float:
+    """Bytes one layer-step must move: per retained token K-page bytes / N + V (2*dh) +
+    position (4), plus 8 bytes of block/bits table per page; queries, outputs and codebooks
+    counted once."""
+    N = lists.page_size
+    tot = 0.0
+    cnt = lists.page_count.long()
+    for s, t in enumerate(tiers.tiers):
+        sel = lists.page_slot == s
+        G = dh // t.g
+        c = cnt[sel]
+        tot += float((8 + 4 * G + (c * G * t.b_theta + 7) // 8 + c * G).sum())
+        tot += float(c.sum()) * (2 * dh + 4)
+    tot += lists.n_pages * 8
+    tot += lists.B * CFG["Hq"] * dh * 2 * 2 + lists.Hkv * sum(dh * (1 << t.b_theta) * 4 for t in tiers.tiers)
+    return tot
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while running."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._stop_evt = index, [], threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        while not self._stop_evt.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5)
+                if out.returncode == 0:
+                    self.rows.append([x.strip() for x in out.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop_evt.wait(0.1)
+
+    def stop(self) -> dict:
+        self._stop_evt.set()
+        self.join(timeout=6)
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names)
+                   if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+class CpuReference:
+    """The oracle's restatement of the reference torch decode path
+    (_compressed_head_attention_batched) on `n_units` (batch row, KV head) units of the
+    benchmark workload, all host threads."""
+
+    def __init__(self, budget: float, n_units: int, threads: int):
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import oracle as orc
+        pkg = importlib.import_module("spherical-kv_b200")
+        torch.set_num_threads(threads)
+        self.orc, self.n_units, self.threads = orc, n_units, threads
+        dh, ctx, Hq, Hkv = CFG["dh"], CFG["ctx"], CFG["Hq"], CFG["Hkv"]
+        self.grp = Hq // Hkv
+        specs = pkg.REFERENCE_TIERS[:2]
+        fr = pkg.synth.budget_fractions(budget)
+        K, V, self.Q, _ = pkg.synth.make_kvq(1, self.grp * n_units, n_units, dh, ctx, seed=0)
+        cbs = pkg.synth.make_codebooks(n_units, dh, specs, seed=1)
+        assign = pkg.synth.make_tier_assign(1, n_units, ctx, fr, seed=2)
+        self.cos, self.sin = orc.rope_tables(ctx + 8, dh)
+        self.units = []
+        for h in range(n_units):
+            tl = []
+            for s, t in enumerate(specs):
+                pos = torch.nonzero(assign[0, h] == t.tier_id).flatten()
+                if pos.numel() == 0:
+                    continue
+                r, th = orc.encode(K[0, pos, h].contiguous(), cbs[s][h])
+                tl.append(dict(r=torch.from_numpy(r), theta=torch.from_numpy(th), positions=pos,
+                               V=V[0, pos, h].half().float(), cb=cbs[s][h]))
+            self.units.append(tl)
+        self.total_units = CFG["B"] * Hkv
+        self.desc = (f"{n_units} of {self.total_units} (batch row, KV head) units at ctx {ctx} per step, "
+                     f"scaled linearly to the full layer-step")
+
+    def step_us(self) -> float:
+        """One pass over the sample; microseconds per full layer-step (scaled)."""
+        t0 = time.perf_counter()
+        for h, tl in enumerate(self.units):
+            self.orc.decode_unit(self.Q[0, h * self.grp:(h + 1) * self.grp], tl, self.cos, self.sin,
+                                 torch.float32)
+        return (time.perf_counter() - t0) / self.n_units * self.total_units * 1e6
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    ref = CpuReference(args.budget, n_units=2, threads=threads)
+    for _ in range(max(1, args.warmup)):
+        ref.step_us()
+    steps = max(1, args.steps)
+    t0 = time.perf_counter()
+    vals = [ref.step_us() for _ in range(steps)]
+    v = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": v * CFG["layers"] / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(args),
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                             "sample": ref.desc},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args) -> dict:
+    return {"workload": f"Llama-3.1-8B decode attention, 32-layer sweep, ctx {CFG['ctx']}, batch "
+                        f"{CFG['B']} per GPU, K budget {args.budget:g} bits/token-head, 16-token pages, "
+                        f"bf16 Q/V/out, int8 radii",
+            "B_per_gpu": CFG["B"], "Hq": CFG["Hq"], "Hkv": CFG["Hkv"], "dh": CFG["dh"], "ctx": CFG["ctx"],
+            "layers": CFG["layers"], "page_size": CFG["page_size"], "budget_bits": args.budget,
+            "l2_policy": "32 distinct layer caches (>= 8 GB) cycled per step: inputs larger than L2",
+            "sharding": "batch rows per GPU, no collective"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--budget", type=float, default=96.0, help="average K bits per token-head")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=CFG["layers"])
+    ap.add_argument("--ctx", type=int, default=CFG["ctx"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    CFG["layers"], CFG["ctx"] = args.layers, args.ctx
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    pkg = importlib.import_module("spherical-kv_b200")
+    B, Hq, Hkv, dh, ctx, NL, N = (CFG[k] for k in ("B", "Hq", "Hkv", "dh", "ctx", "layers", "page_size"))
+    specs = pkg.REFERENCE_TIERS[:2]
+    tiers = pkg.TierSet(dh, specs)
+    fr = pkg.synth.budget_fractions(args.budget)
+    rope = pkg.rope_table(ctx + 8, dh, device=dev)
+
+    # ---- build the 32 layer caches with the encode kernel (seeded, generated on the GPU) ----
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    scale = torch.exp(0.5 * torch.randn(dh, generator=gen, device=dev))
+    caches, enc_ms, alg_bytes, tok_heads = [], [], None, None
+    for layer in range(NL):
+        assign = pkg.synth.make_tier_assign(B, Hkv, ctx, fr, seed=100 + layer).to(dev)
+        lists = pkg.build_page_lists(assign, tiers, N, shuffle_seed=layer)
+        K = (torch.randn(B * ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+        V = (torch.randn(B * ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+        cb = tiers.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs, seed=layer)])
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        cache = pkg.encode_pages(K, V, lists, cb, tiers, v_dtype=torch.bfloat16)
+        e1.record()
+        torch.cuda.synchronize()
+        enc_ms.append(e0.elapsed_time(e1))
+        if alg_bytes is None:
+            alg_bytes = algorithmic_bytes(lists, tiers, dh)
+            tok_heads = int(lists.page_count.sum().item())
+        cache.scratch = pkg.decode_scratch(cache)
+        caches.append(cache)
+        del K, V, assign
+
+    q_host = (torch.randn(NL, B, Hq, dh) * scale.cpu()).bfloat16().pin_memory()
+    q_dev = q_host.to(dev)
+    out_dev = torch.empty(NL, B, Hq, dh, dtype=torch.bfloat16, device=dev)
+    out_host = torch.empty(NL, B, Hq, dh, dtype=torch.bfloat16).pin_memory()
+
+    def sweep():
+        for layer in range(NL):
+            pkg.decode_paged(q_dev[layer], caches[layer], rope, out=out_dev[layer])
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        sweep()
+        sweep()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            sweep()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+                torch.cuda.synchronize()
+
+        def timed(fn, steps):
+            barrier()
+            sampler = ClockSampler(local)
+            sampler.start()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            barrier()
+            ms = e0.elapsed_time(e1)
+            clocks = sampler.stop()
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms, clocks
+
+        # device-resident: the graph of 32 layer-steps.  Clock samples need some wall time, so
+        # run at least ~0.5 s worth of steps but report exactly `steps`.
+        ms, clocks = timed(graph.replay, args.steps)
+
+        def e2e_step():
+            q_dev.copy_(q_host, non_blocking=True)
+            sweep()
+            out_host.copy_(out_dev, non_blocking=True)
+
+        for _ in range(args.warmup):
+            e2e_step()
+        ms_e2e, _ = timed(e2e_step, args.steps)
+
+    ms_per_step = ms / args.steps
+    us_layer = ms_per_step * 1e3 / NL
+    us_layer_e2e = ms_e2e / args.steps * 1e3 / NL
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    achieved = alg_bytes / (us_layer * 1e-6) / 1e9
+    status = sum(int(c.status.item()) for c in caches)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": us_layer, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args),
+            "clocks": clocks,
+            "e2e": {"value": us_layer_e2e, "unit": UNIT, "h2d_bytes_per_step": q_host.numel() * 2,
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "gpu_launches": 3 * NL * args.steps,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": alg_bytes,
+                         "note": "duration = one layer-step (plan + decode + merge kernels) from CUDA "
+                                 "events over the timed region; frac_of_8TBs = %.3f" % (achieved / 8000.0)},
+            "achieved_hbm_gbs_all_gpus": achieved * world,
+            "token_heads_per_layer_step": tok_heads,
+            "encode": {"ms_per_layer": sum(enc_ms[1:]) / max(1, len(enc_ms) - 1),
+                       "token_heads_per_s": tok_heads / (sum(enc_ms[1:]) / max(1, len(enc_ms) - 1) * 1e-3)},
+            "kernel_status": status,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            threads = os.cpu_count() or 1
+            ref = CpuReference(args.budget, n_units=2, threads=threads)
+            ref.step_us()
+            v = min(ref.step_us() for _ in range(3))
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": ref.desc + ", best of 3"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
