@@ -226,10 +226,25 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
         qv = fminf(fmaxf(qv, -127.f), 127.f);
         im[roff + i] = (uint8_t)(int8_t)(int)qv;
       } else {
-        const uint16_t hv = __half_as_ushort(__float2half_rn(rr));
-        im[roff + 2 * i] = (uint8_t)(hv & 0xFF);
-        im[roff + 2 * i + 1] = (uint8_t)(hv >> 8);
+        // stage the half's bit pattern as a 32-bit word over the radius slot (same thread
+        // read it above); the bytes are laid into the page image after the barrier
+        unsigned short hv;
+        asm volatile("cvt.rn.f16.f32 %0, %1;" : "=h"(hv) : "f"(rr));
+        reinterpret_cast<uint32_t*>(r_s)[tbase * G + i] = (uint32_t)hv;
       }
+    }
+  }
+  if (rb == 2) {
+    __syncthreads();
+    for (int q = 0; q < ppb; ++q) {
+      const int cnt = count_s[q];
+      if (cnt == 0) continue;
+      uint8_t* im = img + q * img_stride;
+      const int tbase = N >= 64 ? 0 : q * N;
+      const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
+      const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_s + tbase * G);
+      for (int b = threadIdx.x; b < 2 * cnt * G; b += blockDim.x)
+        im[roff + b] = hb[(b >> 1) * 4 + (b & 1)];
     }
   }
   __syncthreads();

@@ -251,3 +251,23 @@ class PagedCache:
     @property
     def dh(self) -> int:
         return self.tiers.dh
+
+
+def shard_block_lists(lists: PageLists, rank: int, world: int) -> PageLists:
+    """Split-KV view: every unit's logical block list is cut into `world` contiguous ranges
+    and rank `rank` keeps its range (pools and page ids are unchanged, only the tables
+    differ).  Partials of all ranks merged by log-sum-exp equal one pass over the full list."""
+    nb = lists.num_blocks.long()
+    lo = nb * rank // world
+    hi = nb * (rank + 1) // world
+    width = max(1, int((hi - lo).max().item()))
+    cols = lo.unsqueeze(1) + torch.arange(width, device=nb.device).unsqueeze(0)
+    valid = cols < hi.unsqueeze(1)
+    cols = cols.clamp(max=lists.max_blocks - 1)
+    bt = torch.where(valid, torch.gather(lists.block_table, 1, cols), torch.full_like(cols, -1, dtype=torch.int32))
+    st = torch.where(valid, torch.gather(lists.bits_table, 1, cols), torch.zeros_like(cols, dtype=torch.int32))
+    out = PageLists(**lists.__dict__)
+    out.block_table, out.bits_table = bt.to(torch.int32).contiguous(), st.to(torch.int32).contiguous()
+    out.num_blocks = (hi - lo).to(torch.int32)
+    out.max_blocks = width
+    return out

@@ -50,8 +50,10 @@ def check_against_oracle(cache, cbs, Q, ctx, dh, q_dtype=torch.float32, out_dtyp
         cos, sin = torch.ones_like(cos), torch.zeros_like(sin)
     want, want_logits = orc.decode_cache(qd.float().cpu(), cc, cos, sin, torch.float64)
     got = out.float().cpu()
-    # outputs: max-abs after rounding both to bf16
-    d_out = (got.bfloat16().float() - want.float().bfloat16().float()).abs().max().item()
+    # outputs: max-abs <= 2e-3; a bf16 output may additionally be off by its own rounding
+    # (half an ulp, 2^-9 relative)
+    slack = want.float().abs() * 2.0 ** -9 if out_dtype == torch.bfloat16 else 0.0
+    d_out = ((got - want.float()).abs() - slack).max().item()
     assert d_out <= out_tol, d_out
     # logits: |delta| <= 1e-3 * max(|ref|, 0.1*|q||k_hat|/sqrt(dh)), per stored token
     lg = logits.cpu()
@@ -183,39 +185,32 @@ def test_decode_matches_reference_golden_c1():
             kn = Kx[0, pos, h].double().norm(dim=1)
             tol = 1e-3 * torch.maximum(ref_l.abs(), 0.1 * qn * kn[None, :] / dh ** 0.5)
             worst = max(worst, ((g - ref_l).abs() / tol).max().item())
-            d = (out[0, h * grp:(h + 1) * grp].float().cpu().bfloat16().float()
-                 - ref_o.bfloat16().float()).abs().max().item()
+            d = (out[0, h * grp:(h + 1) * grp].float().cpu() - ref_o).abs().max().item()
             assert d <= 2e-3, (name, h, d)
         assert worst <= 1.0, (name, worst)
 
 
-def test_partial_export_and_merge_equals_single_pass():
-    """split the context into 3 contiguous shards (as split-KV ranks would hold them),
-    export (max, sum, acc) per shard, merge -> same as one pass over everything"""
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_partial_export_and_merge_equals_single_pass(world):
+    """split every unit's block list into `world` contiguous shards (what split-KV ranks
+    hold), export (max, sum, acc) per shard, merge -> same as one pass over everything"""
     ctx, dh, Hq, Hkv, B = 900, 128, 8, 2, 2
-    specs = pkg.REFERENCE_TIERS[:2]
-    tiers = pkg.TierSet(dh, specs)
-    K, V, Q, _ = synth.make_kvq(B, Hq, Hkv, dh, ctx, seed=8)
-    cbs = synth.make_codebooks(Hkv, dh, specs, seed=9)
-    assign = synth.make_tier_assign(B, Hkv, ctx, {1: 0.3, 2: 0.5}, seed=10)
+    cache, cbs, K, V, Q, _ = build(B, Hq, Hkv, dh, ctx, 16, pkg.REFERENCE_TIERS[:2], {1: 0.3, 2: 0.5},
+                                   seed=8)
     table = pkg.rope_table(ctx + 8, dh, device=DEV)
-    cbf = tiers.pack_codebooks(cbs).to(DEV)
-    Kd, Vd = K.reshape(B * ctx, Hkv, dh).to(DEV), V.reshape(B * ctx, Hkv, dh).to(DEV)
-
-    def run(mask):
-        a = assign.clone(); a[:, :, ~mask] = 0
-        lists = pkg.build_page_lists(a, tiers, 16, shuffle_seed=2)
-        cache = pkg.encode_pages(Kd, Vd, to_dev(lists), cbf, tiers)
-        part = torch.zeros(B, Hq, dh + 2, device=DEV)
-        out = pkg.decode_paged(Q.to(DEV), cache, table, out_partial=part)
-        return out, part
-
-    full, _ = run(torch.ones(ctx, dtype=torch.bool))
+    qd = Q.to(DEV)
+    full = pkg.decode_paged(qd, cache, table).clone()
     parts = []
-    for lo, hi in ((0, 300), (300, 650), (650, 900)):
-        m = torch.zeros(ctx, dtype=torch.bool); m[lo:hi] = True
-        parts.append(run(m)[1])
-    merged = pkg.merge_partials(torch.stack(parts).reshape(3, B * Hq, dh + 2))
+    for rnk in range(world):
+        sh = pkg.PagedCache(tiers=cache.tiers, lists=pkg.shard_block_lists(cache.lists, rnk, world),
+                            codebooks=cache.codebooks, k_pages=cache.k_pages, v_pool=cache.v_pool,
+                            radius_fmt=cache.radius_fmt)
+        part = torch.zeros(B, Hq, dh + 2, device=DEV)
+        pkg.decode_paged(qd, sh, table, out_partial=part, want_out=False)
+        parts.append(part)
+    nb = cache.lists.num_blocks.cpu()
+    assert sum(int(pkg.shard_block_lists(cache.lists, r, world).num_blocks.sum()) for r in range(world)) == int(nb.sum())
+    merged = pkg.merge_partials(torch.stack(parts).reshape(world, B * Hq, dh + 2).contiguous())
     torch.cuda.synchronize()
     assert (merged.view(B, Hq, dh) - full).abs().max().item() <= 2e-5 * full.abs().max().item() + 1e-6
 
