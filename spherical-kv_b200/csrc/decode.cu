@@ -1,43 +1,48 @@
 // Angle-domain decode attention over bit-packed, paged, codebook-quantised keys.
 //
-// One persistent CTA per SM walks a contiguous range of (batch row, KV head) blocks.
-// Each warp owns every WARPS-th 16-token tile of the range and keeps an online-softmax
+// One persistent CTA per SM (12 warps) walks a contiguous range of (KV head, batch row)
+// blocks.  Each warp owns every 12th 16-token tile of the range and keeps an online-softmax
 // state for all query heads of the KV head.  Per tile a warp
-//   1. unpacks the tile's centroid indices and radii (lane = token x half of groups),
+//   1. unpacks the tile's centroid indices and radii (lane = token x half of the groups),
 //   2. rebuilds the 16 x dh key tile directly in mma A-fragment registers: gathers the
-//      selected centroid rows from shared memory, scales by the radius and rotates by
-//      the key's RoPE angle (cos/sin row of the key position, read through L2),
+//      selected centroid rows from shared memory, scales by the radius and rotates by the
+//      key's RoPE angle (cos/sin row of the key position, read through L2),
 //   3. forms logits with fp16 hi/lo split operands on the tensor cores
 //      (tokens x dh) * (dh x heads), fp32 accumulate,
-//   4. runs the online softmax and accumulates P^T V with V tiles that cp.async streams
+//   4. runs the online softmax and accumulates V^T P^T with V tiles that cp.async streams
 //      into a swizzled shared-memory ring.
-// Warp states are merged per CTA, CTA partials land in scratch, and a small kernel
-// merges them by log-sum-exp.
+// Every global load a tile needs is issued one or two tiles ahead.  Warp states are merged
+// per CTA, CTA partials land in scratch, and a small kernel merges them by log-sum-exp.
 //
 // Numerics restate SphericalKVPipeline._compressed_head_attention_batched
 // (spherical_kv_pipeline.py:2136-2177): logit = sum_g r_g * (q_rot_g . c_g) / sqrt(dh)
-// with q back-rotated by the key position; rotating the rebuilt key forward instead
-// is the same bilinear form.  Page bytes follow pagebuilder.py:8-33 / paging.py:20-31.
+// with q back-rotated by the key position; rotating the rebuilt key forward instead is the
+// same bilinear form.  Page bytes follow pagebuilder.py:8-33 / paging.py:20-31.
 #include <stdarg.h>
-#include <type_traits>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
 namespace sphkv {
 
-constexpr int kWarps = 8;
+constexpr int kWarps = 12;
 constexpr int kVStages = 3;
-constexpr int kMetaRing = 64;
+constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
+constexpr int kMaxUnitsInKernelPlan = 2048;
 
-struct TileMeta {  // 32 bytes
-  int phys;        // physical page id, <0 = nothing to do
-  int slot;        // tier slot
-  int poff, toff, roff;
-  int count;       // tokens in the page
-  int sub;         // 16-token tile index inside the page
-  int lb;          // logical block index inside the unit
+// 16 bytes per tile
+struct TileMeta {
+  int phys;       // physical page id; -1 hole / invalid, -2 past the end
+  int poff;       // page offset in the byte pool
+  int toff;       // theta offset
+  uint32_t misc;  // (radius_off - theta_off) | count << 16 | slot << 24
 };
+__device__ __forceinline__ int meta_count(const TileMeta& m) { return (m.misc >> 16) & 0xFF; }
+__device__ __forceinline__ int meta_slot(const TileMeta& m) { return (m.misc >> 24) & 0x3; }
+__device__ __forceinline__ int meta_roff(const TileMeta& m) { return m.toff + (int)(m.misc & 0xFFFF); }
 
 struct DecodeArgs {
   sphkv_decode_params p;
@@ -46,13 +51,27 @@ struct DecodeArgs {
   int n_units;
   int n_ctas;
   int grp;
+  int plan_in_kernel;  // every CTA derives the block prefix itself (n_units small enough)
   int32_t* pfx;
   float* rows;  // [(n_ctas + n_units)][8][dh + 2]
 };
 
+// shared-memory carve-up, shared by host and device
+__host__ __device__ constexpr int smem_v_bytes(int dh) { return kWarps * kVStages * 16 * dh * 2; }
+__host__ __device__ constexpr int smem_q_bytes(int dh) { return 2 * (dh / 16) * 32 * 8; }
+__host__ __device__ constexpr int smem_priv_bytes(int dh) {
+  return 16 * (dh / 16) * 8 + 512 + kMetaRing * 16;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---- plan: exclusive prefix of blocks per unit --------------------------------------
 __global__ void plan_kernel(const int32_t* __restrict__ num_blocks, int n_units, int max_blocks,
-                            int32_t* __restrict__ pfx) {
+                            int B, int Hkv, int32_t* __restrict__ pfx) {
   __shared__ int s_part[32];
   __shared__ int s_carry;
   if (threadIdx.x == 0) s_carry = 0;
@@ -62,7 +81,7 @@ __global__ void plan_kernel(const int32_t* __restrict__ num_blocks, int n_units,
     int i = base + threadIdx.x;
     int v = 0;
     if (i < n_units) {
-      v = num_blocks[i];
+      v = num_blocks[(i % B) * Hkv + i / B];  // traversal order: KV head major, batch row minor
       v = v < 0 ? 0 : (v > max_blocks ? max_blocks : v);
     }
     int x = v;
@@ -106,16 +125,108 @@ __device__ __forceinline__ int find_unit(const int32_t* pfx, int n, int64_t x) {
   return lo;
 }
 
-template <int DH>
+// words of a K page this lane needs for its (token, half-of-groups) unpack role
 struct KWords {
   uint32_t th0, th1;       // aligned words holding this lane's theta bits
   uint32_t rd0, rd1, rd2;  // aligned words holding this lane's radius bytes
   float sc[4];             // per-group scales of this lane's groups
   int th_sh, rd_sh;        // bit shifts into the funnels
-  int pos0, pos1;          // key positions of rows (lane>>2) and (lane>>2)+8
 };
 
-template <int DH, typename VT>
+// Issue the global loads of one lane's K words.  SPG = 16-dim steps per group (g / 16).
+template <int DH, int SPG>
+__device__ __forceinline__ void load_kwords_t(const sphkv_decode_params& p, const TileMeta& m, int sub,
+                                              int bits, int ut, int uhalf, KWords& w) {
+  constexpr int HS = DH / 32, NG = HS / SPG, G = DH / (16 * SPG);
+  const int tp = 16 * sub + ut;
+  if (tp >= meta_count(m)) return;
+  const int gam0 = uhalf * NG;
+  const int bit = (tp * G + gam0) * bits;
+  const int ba = m.toff + (bit >> 3);
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.k_pages + (ba & ~3));
+  w.th_sh = (ba & 3) * 8 + (bit & 7);
+  w.th0 = wp[0];
+  if (w.th_sh + NG * bits > 32) w.th1 = wp[1];
+  const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
+  const int ra = meta_roff(m) + (tp * G + gam0) * rb;
+  const uint32_t* rp = reinterpret_cast<const uint32_t*>(p.k_pages + (ra & ~3));
+  w.rd_sh = (ra & 3) * 8;
+  const int need = (ra & 3) + NG * rb;  // bytes from the aligned word start
+  w.rd0 = rp[0];
+  if (need > 4) w.rd1 = rp[1];
+  if (need > 8) w.rd2 = rp[2];
+  if (rb == 1) {
+    const float* sp = reinterpret_cast<const float*>(p.k_pages + m.poff + 8) + gam0;
+#pragma unroll
+    for (int i = 0; i < NG; ++i) w.sc[i] = sp[i];
+  }
+}
+
+// Unpack this lane's codes and radii into (codebook row offset, radius) entries, one per
+// 16-dim step: unp[token][step].
+template <int DH, int SPG>
+__device__ __forceinline__ void unpack_t(const KWords& w, const TileMeta& m, int sub, int bits, int fmt,
+                                         uint32_t cbase, int ut, int uhalf, uint2* unp) {
+  constexpr int KS = DH / 16, HS = KS / 2, NG = HS / SPG;
+  const int gam0 = uhalf * NG;
+  const uint32_t cmask = (1u << bits) - 1u;
+  const uint32_t tb = __funnelshift_r(w.th0, w.th1, w.th_sh);
+  const uint32_t rlo = __funnelshift_r(w.rd0, w.rd1, w.rd_sh);
+  const uint32_t rhi = __funnelshift_r(w.rd1, w.rd2, w.rd_sh);
+  const bool tok_ok = (16 * sub + ut) < meta_count(m);
+  uint2 e[NG * SPG];
+#pragma unroll
+  for (int i = 0; i < NG; ++i) {
+    const uint32_t code = (tb >> (i * bits)) & cmask;
+    float rad;
+    if (fmt == SPHKV_RADIUS_F16) {
+      const uint32_t wv = (i < 2) ? rlo : rhi;
+      rad = __half2float(__ushort_as_half((unsigned short)(wv >> ((i & 1) * 16))));
+    } else {
+      const int c8 = (int)(int8_t)((rlo >> (i * 8)) & 0xFFu);
+      rad = (w.sc[i] * (float)c8) * (1.0f / 127.0f);
+    }
+    if (!tok_ok) rad = 0.f;
+    const uint32_t row = (((uint32_t)(gam0 + i) << bits) + code) * SPG;
+#pragma unroll
+    for (int s2 = 0; s2 < SPG; ++s2)
+      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * 64u, __float_as_uint(rad));
+  }
+  uint2* dst = unp + ut * KS + gam0 * SPG;  // 16-byte aligned: KS and NG*SPG are even
+#pragma unroll
+  for (int i = 0; i < NG * SPG; i += 2)
+    *reinterpret_cast<uint4*>(dst + i) = make_uint4(e[i].x, e[i].y, e[i + 1].x, e[i + 1].y);
+}
+
+// rotate one (low-half, high-half) float4 pair by (cos, sin) and split into fp16 hi/lo
+// A-fragment registers
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+template <bool ROT>
+__device__ __forceinline__ void build_pair(float4 x, float4 y, float r0, float r1, const float4& c,
+                                           const float4& sn, int tk, uint32_t (&a_lo_hi)[4],
+                                           uint32_t (&a_lo_lo)[4], uint32_t (&a_hi_hi)[4],
+                                           uint32_t (&a_hi_lo)[4]) {
+  const float2 rr0 = f2(r0, r0), rr1 = f2(r1, r1);
+  float2 x0 = __fmul2_rn(f2(x.x, x.y), rr0), x1 = __fmul2_rn(f2(x.z, x.w), rr0);
+  float2 y0 = __fmul2_rn(f2(y.x, y.y), rr1), y1 = __fmul2_rn(f2(y.z, y.w), rr1);
+  float2 lo0 = x0, lo1 = x1, hi0 = y0, hi1 = y1;
+  if (ROT) {
+    const float2 c0 = f2(c.x, c.y), c1 = f2(c.z, c.w);
+    const float2 s0 = f2(sn.x, sn.y), s1 = f2(sn.z, sn.w);
+    const float2 n0 = f2(-sn.x, -sn.y), n1 = f2(-sn.z, -sn.w);
+    lo0 = __ffma2_rn(y0, n0, __fmul2_rn(x0, c0));
+    lo1 = __ffma2_rn(y1, n1, __fmul2_rn(x1, c1));
+    hi0 = __ffma2_rn(x0, s0, __fmul2_rn(y0, c0));
+    hi1 = __ffma2_rn(x1, s1, __fmul2_rn(y1, c1));
+  }
+  split_f16x2(lo0.x, lo0.y, a_lo_hi[tk], a_lo_lo[tk]);
+  split_f16x2(lo1.x, lo1.y, a_lo_hi[2 + tk], a_lo_lo[2 + tk]);
+  split_f16x2(hi0.x, hi0.y, a_hi_hi[tk], a_hi_lo[tk]);
+  split_f16x2(hi1.x, hi1.y, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
+}
+
+template <int DH, typename VT, bool ROT, bool EXTRA>
 __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const DecodeArgs a) {
   constexpr int KS = DH / 16;  // 16-dim steps over the head dim
   constexpr int HS = KS / 2;   // steps in one rotary half
@@ -127,15 +238,51 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   const sphkv_decode_params& p = a.p;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
+  const int ut = lane >> 1, uhalf = lane & 1;  // unpack role: token, half of the groups
 
   uint8_t* v_ring = smem + warp * V_WARP;
-  uint8_t* cb_smem = smem + kWarps * V_WARP;
-  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + warp * (16 * KS * 8 + 512 + kMetaRing * 32);
+  uint8_t* cb_smem = smem + smem_v_bytes(DH);
+  uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [2][KS][32]
+  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) + warp * smem_priv_bytes(DH);
   uint2* unp = reinterpret_cast<uint2*>(warp_priv);                       // [16][KS]
   uint16_t* pbuf = reinterpret_cast<uint16_t*>(warp_priv + 16 * KS * 8);  // [2][8][16]
   TileMeta* meta = reinterpret_cast<TileMeta*>(warp_priv + 16 * KS * 8 + 512);
 
-  const int32_t* __restrict__ pfx = a.pfx;
+  // ---- block prefix per unit: computed by warp 0 of every CTA (CTA 0 publishes it for the
+  //      merge kernel), or read from the plan kernel's output when there are many units ----
+  const int32_t* pfx = a.pfx;
+  if (a.plan_in_kernel) {
+    int32_t* pfx_s = reinterpret_cast<int32_t*>(cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) +
+                                                kWarps * smem_priv_bytes(DH));
+    if (warp == 0) {
+      int carry = 0;
+      for (int base = 0; base < a.n_units; base += 32) {
+        const int i = base + lane;
+        int v = 0;
+        if (i < a.n_units) {
+          v = p.num_blocks[(i % p.B) * p.Hkv + i / p.B];
+          v = v < 0 ? 0 : (v > p.max_blocks ? p.max_blocks : v);
+        }
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int y = __shfl_up_sync(0xffffffffu, x, o);
+          if (lane >= o) x += y;
+        }
+        if (i < a.n_units) {
+          pfx_s[i] = carry + x - v;
+          if (blockIdx.x == 0) a.pfx[i] = carry + x - v;
+        }
+        carry += __shfl_sync(0xffffffffu, x, 31);
+      }
+      if (lane == 0) {
+        pfx_s[a.n_units] = carry;
+        if (blockIdx.x == 0) a.pfx[a.n_units] = carry;
+      }
+    }
+    __syncthreads();
+    pfx = pfx_s;
+  }
   const int64_t T = pfx[a.n_units];
   if (T == 0) return;
   int64_t start = cta_range_start(blockIdx.x, a.n_ctas, T);
@@ -145,8 +292,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
   const int N = p.page_size;
   const int TPP = N >> 4;
-  const bool rot = p.rope_table != nullptr;
   const float qscale = p.sm_scale * kLog2e;
+  const int fmt = p.radius_fmt;
   int cb_head_loaded = -1;
 
   while (start < end) {
@@ -154,154 +301,116 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
     const int64_t seg_end = end < (int64_t)pfx[u + 1] ? end : (int64_t)pfx[u + 1];
     const int lb0 = (int)(start - pfx[u]);
     const int seg_tiles = (int)(seg_end - start) * TPP;
-    const int b = u / p.Hkv, hkv = u - b * p.Hkv;
-
-    // ---- stage this KV head's codebooks (permuted for lane-quad float4 reads) ----
-    __syncthreads();
-    if (hkv != cb_head_loaded) {
-      const sphkv_tiers& tg = p.tiers;
-      for (int s = 0; s < tg.n_slots; ++s) {
-        const int g = tg.g[s], C = 1 << tg.bits[s], G = DH / g, spg = g >> 4;
-        const float* src =
-            p.codebooks + ((int64_t)(hkv * tg.n_slots + s) * tg.G_max) * tg.C_max * tg.g_max;
-        float* dst = reinterpret_cast<float*>(cb_smem + a.cb_smem_off[s]);
-        const int total = G * C * g;
-        for (int i = threadIdx.x; i < total; i += blockDim.x) {
-          const int e = i & 3, jj = (i >> 2) & 3, row = i >> 4;
-          const int sub2 = row % spg, gc = row / spg;
-          const int c = gc % C, gam = gc / C;
-          const int d = sub2 * 16 + 2 * jj + (e & 1) + ((e >> 1) << 3);
-          dst[i] = src[((int64_t)gam * tg.C_max + c) * tg.g_max + d];
-        }
-      }
-      cb_head_loaded = hkv;
-    }
-    __syncthreads();
-
-    // ---- query fragments: B operand [k = dim][n = head], fp16 hi/lo, pre-scaled ----
-    uint32_t qhi[KS][2], qlo[KS][2];
-    {
-      const int n = r;  // head column of this lane
-      const bool real = n < a.grp;
-      const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * DH;
-#pragma unroll
-      for (int s = 0; s < KS; ++s) {
-        float v[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int d = 16 * s + 2 * j + (e & 1) + ((e >> 1) << 3);
-          v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
-        }
-        split_f16x2(v[0], v[1], qhi[s][0], qlo[s][0]);
-        split_f16x2(v[2], v[3], qhi[s][1], qlo[s][1]);
-      }
-    }
-
+    // units are walked KV head major (u = hkv * B + b) so that neighbouring segments share
+    // their codebooks; tables are indexed by the external unit id b * Hkv + hkv
+    const int hkv = u / p.B, b = u - hkv * p.B;
+    const int u_ext = b * p.Hkv + hkv;
     const int nt = seg_tiles > warp ? (seg_tiles - warp + kWarps - 1) / kWarps : 0;
-    const int32_t* bt_row = p.block_table + (int64_t)u * p.max_blocks;
-    const int32_t* st_row = p.bits_table + (int64_t)u * p.max_blocks;
+    const int32_t* bt_row = p.block_table + (int64_t)u_ext * p.max_blocks;
+    const int32_t* st_row = p.bits_table + (int64_t)u_ext * p.max_blocks;
 
-    auto meta_fill = [&](int kbase) {
+    auto tile_lb = [&](int kk) { return lb0 + (warp + kWarps * kk) / TPP; };
+    auto tile_sub = [&](int kk) { return (warp + kWarps * kk) % TPP; };
+
+    // Tile metadata is fetched 16 tiles at a time, lane = tile (lanes 0..15).  The three
+    // dependent loads (block table -> pointer table -> page header) are issued in separate
+    // loop iterations so that no iteration waits for a load it issued itself.
+    int mf_phys = -2, mf_slot = 0, mf_poff = 0, mf_toff = 0, mf_roff = 0;
+    auto meta_stage0 = [&](int kbase) {
       const int kk = kbase + lane;
-      TileMeta m;
-      m.phys = -2; m.slot = 0; m.poff = m.toff = m.roff = 0; m.count = 0; m.sub = 0; m.lb = 0;
-      if (kk < nt) {
-        const int ti = warp + kWarps * kk;
-        m.lb = lb0 + ti / TPP;
-        m.sub = ti - (ti / TPP) * TPP;
-        int phys = bt_row[m.lb];
-        int slot = st_row[m.lb];
-        if (phys >= p.n_pages) {
-          if (p.status) atomicOr(p.status, SPHKV_ST_BAD_BLOCK);
-          phys = -1;
-        }
-        if (slot < 0 || slot >= p.tiers.n_slots) {
-          if (p.status) atomicOr(p.status, SPHKV_ST_BAD_SLOT);
-          phys = -1;
-          slot = 0;
-        }
-        m.slot = slot;
-        if (phys >= 0) {
-          m.poff = p.ptable[3 * (int64_t)phys + 0];
-          m.toff = p.ptable[3 * (int64_t)phys + 1];
-          m.roff = p.ptable[3 * (int64_t)phys + 2];
-          const uint32_t hdr = *reinterpret_cast<const uint32_t*>(p.k_pages + m.poff);
-          m.count = (int)((hdr >> 8) & 0xFFu);
-          if (m.count > N) m.count = N;
-        }
-        m.phys = phys < 0 ? -1 : phys;
+      mf_phys = -2; mf_slot = 0; mf_poff = mf_toff = mf_roff = 0;
+      if (lane < 16 && kk < nt) {
+        const int lb = tile_lb(kk);
+        mf_phys = bt_row[lb];
+        mf_slot = st_row[lb];
       }
-      meta[kk & (kMetaRing - 1)] = m;
+    };
+    auto meta_stage1 = [&]() {
+      if (mf_phys == -2) return;
+      if (mf_phys >= p.n_pages) {
+        if (p.status) atomicOr(p.status, SPHKV_ST_BAD_BLOCK);
+        mf_phys = -1;
+      }
+      if (mf_slot < 0 || mf_slot >= p.tiers.n_slots) {
+        if (p.status) atomicOr(p.status, SPHKV_ST_BAD_SLOT);
+        mf_phys = -1;
+        mf_slot = 0;
+      }
+      if (mf_phys < 0) { mf_phys = -1; return; }
+      mf_poff = p.ptable[3 * (int64_t)mf_phys + 0];
+      mf_toff = p.ptable[3 * (int64_t)mf_phys + 1];
+      mf_roff = p.ptable[3 * (int64_t)mf_phys + 2];
+    };
+    auto meta_stage2 = [&](int kbase) {
+      if (lane >= 16) return;
+      TileMeta m;
+      m.phys = mf_phys; m.poff = mf_poff; m.toff = mf_toff;
+      int count = 0;
+      if (mf_phys >= 0) {
+        const uint32_t hdr = *reinterpret_cast<const uint32_t*>(p.k_pages + mf_poff);
+        count = (int)((hdr >> 8) & 0xFFu);
+        if (count > N) count = N;
+      }
+      m.misc = (uint32_t)((mf_roff - mf_toff) & 0xFFFF) | ((uint32_t)count << 16) | ((uint32_t)mf_slot << 24);
+      meta[(kbase + lane) & (kMetaRing - 1)] = m;
+    };
+    auto get_meta = [&](int kk) -> TileMeta {
+      const uint4 v = *reinterpret_cast<const uint4*>(&meta[kk & (kMetaRing - 1)]);
+      TileMeta m;
+      m.phys = (int)v.x; m.poff = (int)v.y; m.toff = (int)v.z; m.misc = v.w;
+      return m;
     };
 
     auto issue_v = [&](int kk) {
       if (kk < nt) {
-        const TileMeta m = meta[kk & (kMetaRing - 1)];
+        const TileMeta m = get_meta(kk);
         if (m.phys >= 0) {
           const uint8_t* src = reinterpret_cast<const uint8_t*>(p.v_pool) +
-                               ((int64_t)m.phys * N + 16 * m.sub) * DH * 2;
+                               ((int64_t)m.phys * N + 16 * tile_sub(kk)) * DH * 2;
           const uint32_t dst = smem_u32(v_ring + (kk % kVStages) * V_TILE);
 #pragma unroll
           for (int q = 0; q < (16 * DH / 8) / 32; ++q) {
             const int i = lane + 32 * q;
             const int tau = i / (DH / 8), c = i % (DH / 8);
-            const uint32_t d =
-                dst + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4);
-            cp_async_16(d, src + ((int64_t)tau * DH + c * 8) * 2);
+            cp_async_16(dst + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4),
+                        src + (tau * DH + c * 8) * 2);
           }
         }
       }
       cp_async_commit();
     };
 
-    // lane = (token t = lane>>1, half = lane&1) for the unpack role
-    const int ut = lane >> 1, uhalf = lane & 1;
-
-    auto load_kwords = [&](int kk, KWords<DH>& w) {
+    auto load_kwords = [&](int kk, KWords& w) {
       w.th0 = w.th1 = w.rd0 = w.rd1 = w.rd2 = 0u;
       w.th_sh = w.rd_sh = 0;
-      w.pos0 = w.pos1 = -1;
 #pragma unroll
       for (int i = 0; i < 4; ++i) w.sc[i] = 0.f;
       if (kk >= nt) return;
-      const TileMeta m = meta[kk & (kMetaRing - 1)];
+      const TileMeta m = get_meta(kk);
       if (m.phys < 0) return;
-      const int g = p.tiers.g[m.slot], bits = p.tiers.bits[m.slot];
-      const int G = DH / g, spg = g >> 4, ng = HS / spg, gam0 = uhalf * ng;
-      const int tp = 16 * m.sub + ut;
-      if (tp < m.count) {
-        const int64_t bit = ((int64_t)tp * G + gam0) * bits;
-        const int64_t ba = (int64_t)m.toff + (bit >> 3);
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.k_pages + (ba & ~3LL));
-        w.th_sh = (int)((ba & 3) * 8 + (bit & 7));
-        w.th0 = wp[0];
-        if (w.th_sh + ng * bits > 32) w.th1 = wp[1];
-        const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-        const int64_t ra = (int64_t)m.roff + ((int64_t)tp * G + gam0) * rb;
-        const uint32_t* rp = reinterpret_cast<const uint32_t*>(p.k_pages + (ra & ~3LL));
-        w.rd_sh = (int)((ra & 3) * 8);
-        const int need = (int)(ra & 3) + ng * rb;  // bytes from the aligned word start
-        w.rd0 = rp[0];
-        if (need > 4) w.rd1 = rp[1];
-        if (need > 8) w.rd2 = rp[2];
-        const float* sp = reinterpret_cast<const float*>(p.k_pages + m.poff + 8) + gam0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (i < ng) w.sc[i] = sp[i];
-      }
-      if (rot) {
-        const int32_t* pp = p.positions + (int64_t)m.phys * N + 16 * m.sub;
-        w.pos0 = pp[r];
-        w.pos1 = pp[r + 8];
-      }
+      const int slot = meta_slot(m);
+      if (p.tiers.g[slot] == 16)
+        load_kwords_t<DH, 1>(p, m, tile_sub(kk), p.tiers.bits[slot], ut, uhalf, w);
+      else
+        load_kwords_t<DH, 2>(p, m, tile_sub(kk), p.tiers.bits[slot], ut, uhalf, w);
+    };
+    // key positions of rows r and r+8 of tile kk (-1: no token)
+    auto load_pos = [&](int kk, int (&ps)[2]) {
+      ps[0] = ps[1] = -1;
+      if (!ROT || kk >= nt) return;
+      const TileMeta m = get_meta(kk);
+      if (m.phys < 0) return;
+      const int32_t* pp = p.positions + (int64_t)m.phys * N + 16 * tile_sub(kk);
+      ps[0] = pp[r];
+      ps[1] = pp[r + 8];
     };
 
     float4 cs[2][HS][2];
-    auto issue_cs = [&](const KWords<DH>& w) {
-      if (!rot) return;
+    auto issue_cs = [&](const int (&ps)[2]) {
+      if constexpr (ROT) {
 #pragma unroll
       for (int tk = 0; tk < 2; ++tk) {
-        int pos = tk ? w.pos1 : w.pos0;
+        int pos = ps[tk];
         if (pos >= p.max_pos) {
           if (p.status) atomicOr(p.status, SPHKV_ST_BAD_POSITION);
           pos = 0;
@@ -314,6 +423,55 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           cs[tk][s][1] = __ldg(rp + s * 8 + 1);
         }
       }
+      }
+    };
+
+    auto stage_codebooks = [&]() {
+      if (hkv == cb_head_loaded) return;
+      const sphkv_tiers& tg = p.tiers;
+      for (int s = 0; s < tg.n_slots; ++s) {
+        // one thread per 16-dim sub-row: four 128-bit loads, four 128-bit stores in the
+        // lane-quad order (2j, 2j+1, 2j+8, 2j+9)
+        const int g = tg.g[s], bits = tg.bits[s], G = DH / g, spg = g >> 4;
+        const float* src =
+            p.codebooks + ((int64_t)(hkv * tg.n_slots + s) * tg.G_max) * tg.C_max * tg.g_max;
+        float4* dst = reinterpret_cast<float4*>(cb_smem + a.cb_smem_off[s]);
+        const int rows = (G << bits) * spg;
+#pragma unroll 2
+        for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+          const int sub2 = row & (spg - 1), gc = row / spg;
+          const int c = gc & ((1 << bits) - 1), gam = gc >> bits;
+          const float4* sp = reinterpret_cast<const float4*>(
+              src + ((int64_t)gam * tg.C_max + c) * tg.g_max + sub2 * 16);
+          const float4 v0 = __ldg(sp), v1 = __ldg(sp + 1), v2 = __ldg(sp + 2), v3 = __ldg(sp + 3);
+          dst[row * 4 + 0] = make_float4(v0.x, v0.y, v2.x, v2.y);
+          dst[row * 4 + 1] = make_float4(v0.z, v0.w, v2.z, v2.w);
+          dst[row * 4 + 2] = make_float4(v1.x, v1.y, v3.x, v3.y);
+          dst[row * 4 + 3] = make_float4(v1.z, v1.w, v3.z, v3.w);
+        }
+      }
+      cb_head_loaded = hkv;
+    };
+
+    // query fragments, B operand [k = dim][n = head], fp16 hi/lo, pre-scaled by
+    // sm_scale * log2(e); one copy per CTA in shared memory: q_smem[hl][step][lane]
+    auto stage_q = [&]() {
+      for (int i = threadIdx.x; i < KS * 32; i += blockDim.x) {
+        const int s = i >> 5, ln = i & 31, n = ln >> 2, jj = ln & 3;
+        const bool real = n < a.grp;
+        const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * DH;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int d = 16 * s + 2 * jj + (e & 1) + ((e >> 1) << 3);
+          v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
+        }
+        uint2 hi, lo;
+        split_f16x2(v[0], v[1], hi.x, lo.x);
+        split_f16x2(v[2], v[3], hi.y, lo.y);
+        q_smem[i] = hi;
+        q_smem[KS * 32 + i] = lo;
+      }
     };
 
     // online-softmax state: this lane's two head columns (2j, 2j+1)
@@ -325,60 +483,47 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[dt][e] = 0.f;
 
-    // ---- prologue -------------------------------------------------------------------
-    meta_fill(0);
-    meta_fill(32);
-    __syncwarp();
+    // ---- prologue: the block-table -> pointer-table -> header chain of the first 16 tiles
+    //      is interleaved with the codebook and query loads so their latencies overlap ----
+    __syncthreads();  // the previous segment is done with shared memory
+    meta_stage0(0);
+    stage_codebooks();
+    meta_stage1();
+    stage_q();
+    meta_stage2(0);
+    __syncthreads();
     issue_v(0);
     issue_v(1);
-    KWords<DH> cur, nx;
+    KWords cur, nx;
+    int pos_c[2], pos_1[2], pos_2[2];  // positions of tiles k, k+1, k+2
     load_kwords(0, cur);
-    issue_cs(cur);
+    load_pos(0, pos_c);
+    load_pos(1, pos_1);
+    issue_cs(pos_c);
 
     for (int k = 0; k < nt; ++k) {
-      if (k > 0 && (k & 31) == 0) {
-        meta_fill(k + 32);
-        __syncwarp();
+      {  // fetch the next 16 tiles' metadata into the idle half of the ring, in three steps
+        const int ph = k & 15, kb = (k & ~15) + 16;
+        if (ph == 0) meta_stage0(kb);
+        else if (ph == 5) meta_stage1();
+        else if (ph == 10) { meta_stage2(kb); __syncwarp(); }
       }
       issue_v(k + 2);
       load_kwords(k + 1, nx);
-      const TileMeta m = meta[k & (kMetaRing - 1)];
-      const int cnt_tile = m.phys < 0 ? 0 : min(16, max(0, m.count - 16 * m.sub));
+      load_pos(k + 2, pos_2);
+      const TileMeta m = get_meta(k);
+      const int sub = tile_sub(k);
+      const int cnt_tile = m.phys < 0 ? 0 : min(16, max(0, meta_count(m) - 16 * sub));
 
       if (cnt_tile > 0) {
         // ---- phase A: unpack codes/radii of (token ut, half uhalf) ------------------
         {
-          const int g = p.tiers.g[m.slot], bits = p.tiers.bits[m.slot];
-          const int C = 1 << bits, spg = g >> 4, ng = HS / spg, gam0 = uhalf * ng;
-          const uint32_t cbase = (uint32_t)a.cb_smem_off[m.slot];
-          const uint32_t tb = __funnelshift_r(cur.th0, cur.th1, cur.th_sh);
-          const uint32_t rlo = __funnelshift_r(cur.rd0, cur.rd1, cur.rd_sh);
-          const uint32_t rhi = __funnelshift_r(cur.rd1, cur.rd2, cur.rd_sh);
-          const bool tok_ok = (16 * m.sub + ut) < m.count;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            if (i < ng) {
-              const int code = (int)((tb >> (i * bits)) & (uint32_t)(C - 1));
-              float rad;
-              if (p.radius_fmt == SPHKV_RADIUS_F16) {
-                const uint32_t wv = (i < 2) ? rlo : rhi;
-                const uint16_t hv = (uint16_t)(wv >> ((i & 1) * 16));
-                rad = __half2float(__ushort_as_half(hv));
-              } else {
-                const int c8 = (int)(int8_t)((rlo >> (i * 8)) & 0xFFu);
-                rad = (cur.sc[i] * (float)c8) * (1.0f / 127.0f);
-              }
-              if (!tok_ok) rad = 0.f;
-              const int gam = gam0 + i;
-#pragma unroll
-              for (int s2 = 0; s2 < 2; ++s2) {
-                if (s2 < spg) {
-                  const uint32_t off = cbase + (uint32_t)(((gam * C + code) * spg + s2) * 64);
-                  unp[ut * KS + gam * spg + s2] = make_uint2(off, __float_as_uint(rad));
-                }
-              }
-            }
-          }
+          const int slot = meta_slot(m);
+          const uint32_t cbase = (uint32_t)a.cb_smem_off[slot];
+          if (p.tiers.g[slot] == 16)
+            unpack_t<DH, 1>(cur, m, sub, p.tiers.bits[slot], fmt, cbase, ut, uhalf, unp);
+          else
+            unpack_t<DH, 2>(cur, m, sub, p.tiers.bits[slot], fmt, cbase, ut, uhalf, unp);
         }
         __syncwarp();
 
@@ -393,49 +538,39 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             const int tau = r + 8 * tk;
             const uint2 e0 = unp[tau * KS + s];
             const uint2 e1 = unp[tau * KS + s + HS];
-            float4 x = *reinterpret_cast<const float4*>(cb_smem + e0.x + j * 16);
-            float4 y = *reinterpret_cast<const float4*>(cb_smem + e1.x + j * 16);
-            const float r0 = __uint_as_float(e0.y), r1 = __uint_as_float(e1.y);
-            x.x *= r0; x.y *= r0; x.z *= r0; x.w *= r0;
-            y.x *= r1; y.y *= r1; y.z *= r1; y.w *= r1;
-            float4 lo = x, hi = y;
-            if (rot) {
-              const float4 c = cs[tk][s][0], sn = cs[tk][s][1];
-              lo.x = x.x * c.x - y.x * sn.x; hi.x = y.x * c.x + x.x * sn.x;
-              lo.y = x.y * c.y - y.y * sn.y; hi.y = y.y * c.y + x.y * sn.y;
-              lo.z = x.z * c.z - y.z * sn.z; hi.z = y.z * c.z + x.z * sn.z;
-              lo.w = x.w * c.w - y.w * sn.w; hi.w = y.w * c.w + x.w * sn.w;
-            }
-            split_f16x2(lo.x, lo.y, a_lo_hi[tk], a_lo_lo[tk]);
-            split_f16x2(lo.z, lo.w, a_lo_hi[2 + tk], a_lo_lo[2 + tk]);
-            split_f16x2(hi.x, hi.y, a_hi_hi[tk], a_hi_lo[tk]);
-            split_f16x2(hi.z, hi.w, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
+            const float4 x = *reinterpret_cast<const float4*>(cb_smem + e0.x + j * 16);
+            const float4 y = *reinterpret_cast<const float4*>(cb_smem + e1.x + j * 16);
+            build_pair<ROT>(x, y, __uint_as_float(e0.y), __uint_as_float(e1.y), cs[tk][s][0],
+                            cs[tk][s][1], tk, a_lo_hi, a_lo_lo, a_hi_hi, a_hi_lo);
           }
-          mma_f16_16816(s_hh, a_lo_hi, qhi[s][0], qhi[s][1]);
-          mma_f16_16816(s_lh, a_lo_lo, qhi[s][0], qhi[s][1]);
-          mma_f16_16816(s_hl, a_lo_hi, qlo[s][0], qlo[s][1]);
-          mma_f16_16816(s_hh, a_hi_hi, qhi[s + HS][0], qhi[s + HS][1]);
-          mma_f16_16816(s_lh, a_hi_lo, qhi[s + HS][0], qhi[s + HS][1]);
-          mma_f16_16816(s_hl, a_hi_hi, qlo[s + HS][0], qlo[s + HS][1]);
+          const uint2 qh0 = q_smem[s * 32 + lane], ql0 = q_smem[(KS + s) * 32 + lane];
+          const uint2 qh1 = q_smem[(s + HS) * 32 + lane], ql1 = q_smem[(KS + s + HS) * 32 + lane];
+          mma_f16_16816(s_hh, a_lo_hi, qh0.x, qh0.y);
+          mma_f16_16816(s_lh, a_lo_lo, qh0.x, qh0.y);
+          mma_f16_16816(s_hl, a_lo_hi, ql0.x, ql0.y);
+          mma_f16_16816(s_hh, a_hi_hi, qh1.x, qh1.y);
+          mma_f16_16816(s_lh, a_hi_lo, qh1.x, qh1.y);
+          mma_f16_16816(s_hl, a_hi_hi, ql1.x, ql1.y);
         }
         // the cos/sin registers are free now: fetch the next tile's rows
-        issue_cs(nx);
+        issue_cs(pos_1);
 
         // ---- online softmax over the 16 token rows, per head column ------------------
         float sv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) sv[e] = s_hh[e] + (s_lh[e] + s_hl[e]);
-        if (p.logits_out != nullptr) {
+        if (EXTRA && p.logits_out != nullptr) {
+          const int lb = tile_lb(k);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int n = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
             if (n < a.grp && tok < cnt_tile)
-              p.logits_out[(((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + m.lb) * N +
-                           16 * m.sub + tok] = sv[e] * kLn2;
+              p.logits_out[(((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + lb) * N +
+                           16 * sub + tok] = sv[e] * kLn2;
           }
         }
-        const bool ok0 = r < cnt_tile && (!rot || cur.pos0 >= 0);
-        const bool ok1 = (r + 8) < cnt_tile && (!rot || cur.pos1 >= 0);
+        const bool ok0 = r < cnt_tile && (!ROT || pos_c[0] >= 0);
+        const bool ok1 = (r + 8) < cnt_tile && (!ROT || pos_c[1] >= 0);
         if (!ok0) sv[0] = sv[1] = -INFINITY;
         if (!ok1) sv[2] = sv[3] = -INFINITY;
         float tmax[2] = {fmaxf(sv[0], sv[2]), fmaxf(sv[1], sv[3])};
@@ -449,14 +584,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         for (int c = 0; c < 2; ++c) {
           const float mn = fmaxf(m_run[c], tmax[c]);
           msafe[c] = (mn == -INFINITY) ? 0.f : mn;
-          alpha[c] = exp2f(m_run[c] - msafe[c]);
+          alpha[c] = fast_exp2(m_run[c] - msafe[c]);
           m_run[c] = mn;
         }
         float pv[4];
-        pv[0] = exp2f(sv[0] - msafe[0]);
-        pv[1] = exp2f(sv[1] - msafe[1]);
-        pv[2] = exp2f(sv[2] - msafe[0]);
-        pv[3] = exp2f(sv[3] - msafe[1]);
+        pv[0] = fast_exp2(sv[0] - msafe[0]);
+        pv[1] = fast_exp2(sv[1] - msafe[1]);
+        pv[2] = fast_exp2(sv[2] - msafe[0]);
+        pv[3] = fast_exp2(sv[3] - msafe[1]);
         l_run[0] = l_run[0] * alpha[0] + (pv[0] + pv[2]);
         l_run[1] = l_run[1] * alpha[1] + (pv[1] + pv[3]);
         if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
@@ -466,7 +601,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             acc[dt][2] *= alpha[0]; acc[dt][3] *= alpha[1];
           }
         }
-        if (p.page_ml != nullptr && TPP == 1) {
+        if (EXTRA && p.page_ml != nullptr && TPP == 1) {
           // per-block (max, sum) in the natural-log domain for heads 2j, 2j+1
           float ls[2] = {pv[0] + pv[2], pv[1] + pv[3]};
 #pragma unroll
@@ -479,11 +614,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             for (int c = 0; c < 2; ++c) {
               const int n = 2 * j + c;
               if (n < a.grp) {
-                float* dst = p.page_ml +
-                             (((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + m.lb) * 2;
+                float* dst = p.page_ml + (((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks +
+                                          tile_lb(k)) * 2;
                 const float tm = tmax[c];
                 dst[0] = tm * kLn2;
-                dst[1] = (tm == -INFINITY) ? 0.f : ls[c] * exp2f(msafe[c] - tm);
+                dst[1] = (tm == -INFINITY) ? 0.f : ls[c] * fast_exp2(msafe[c] - tm);
               }
             }
           }
@@ -537,11 +672,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         }
         __syncwarp();
       } else {
-        issue_cs(nx);
+        issue_cs(pos_1);
         cp_async_wait<2>();
         __syncwarp();
       }
       cur = nx;
+      pos_c[0] = pos_1[0]; pos_c[1] = pos_1[1];
+      pos_1[0] = pos_2[0]; pos_1[1] = pos_2[1];
     }
     cp_async_wait<0>();
 
@@ -587,7 +724,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             for (int w = 0; w < kWarps; ++w) {
               const float* wb = reinterpret_cast<const float*>(smem + w * V_WARP) + n * (DH + 2);
               const float mw = wb[0];
-              if (mw != -INFINITY) outv += wb[e] * exp2f(mw - M);
+              if (mw != -INFINITY) outv += wb[e] * fast_exp2(mw - M);
             }
           }
         }
@@ -599,43 +736,91 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   }
 }
 
-// ---- merge CTA partial rows per (batch row, KV head) -------------------------------------
 template <int DH>
-__global__ void merge_rows_kernel(const DecodeArgs a) {
+__global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
+  constexpr int kChunk = 128;  // partial rows combined per pass
   const sphkv_decode_params& p = a.p;
-  const int u = blockIdx.x;
-  const int b = u / p.Hkv, hkv = u - b * p.Hkv;
+  const int u = blockIdx.x;  // traversal index: hkv * B + b
+  const int hkv = u / p.B, b = u - hkv * p.B;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __shared__ int s_c[2];
+  __shared__ float s_M[8], s_L[8];
+  __shared__ float s_w[8][kChunk];
   const int32_t* pfx = a.pfx;
   const int64_t T = pfx[a.n_units];
   const int64_t ps = pfx[u], pe = pfx[u + 1];
-  int c_lo = 0, c_hi = -1;
-  if (pe > ps && T > 0) {
-    c_lo = (int)((ps * a.n_ctas) / T);
-    if (c_lo >= a.n_ctas) c_lo = a.n_ctas - 1;
-    while (c_lo > 0 && cta_range_start(c_lo, a.n_ctas, T) > ps) --c_lo;
-    while (cta_range_start(c_lo + 1, a.n_ctas, T) <= ps) ++c_lo;
-    c_hi = c_lo;
-    while (c_hi + 1 < a.n_ctas && cta_range_start(c_hi + 1, a.n_ctas, T) < pe) ++c_hi;
-  }
-  for (int i = threadIdx.x; i < a.grp * DH; i += blockDim.x) {
-    const int n = i / DH, d = i - n * DH;
-    float M = -INFINITY;
-    for (int c = c_lo; c <= c_hi; ++c) {
-      if (cta_range_start(c, a.n_ctas, T) == cta_range_start(c + 1, a.n_ctas, T)) continue;
-      M = fmaxf(M, a.rows[((int64_t)(c + u) * 8 + n) * (DH + 2)]);
+  if (threadIdx.x == 0) {
+    int c_lo = 0, c_hi = -1;
+    if (pe > ps && T > 0) {
+      c_lo = (int)((ps * a.n_ctas) / T);
+      if (c_lo >= a.n_ctas) c_lo = a.n_ctas - 1;
+      while (c_lo > 0 && cta_range_start(c_lo, a.n_ctas, T) > ps) --c_lo;
+      while (cta_range_start(c_lo + 1, a.n_ctas, T) <= ps) ++c_lo;
+      c_hi = (int)(((pe - 1) * a.n_ctas) / T);
+      if (c_hi >= a.n_ctas) c_hi = a.n_ctas - 1;
+      while (c_hi > c_lo && cta_range_start(c_hi, a.n_ctas, T) >= pe) --c_hi;
+      while (c_hi + 1 < a.n_ctas && cta_range_start(c_hi + 1, a.n_ctas, T) < pe) ++c_hi;
     }
-    float l = 0.f, o = 0.f;
-    if (M != -INFINITY) {
-      for (int c = c_lo; c <= c_hi; ++c) {
-        if (cta_range_start(c, a.n_ctas, T) == cta_range_start(c + 1, a.n_ctas, T)) continue;
-        const float* row = a.rows + ((int64_t)(c + u) * 8 + n) * (DH + 2);
-        const float mw = row[0];
-        if (mw == -INFINITY) continue;
-        const float w = exp2f(mw - M);
-        l += row[1] * w;
-        o += row[2 + d] * w;
+    s_c[0] = c_lo;
+    s_c[1] = c_hi;
+  }
+  __syncthreads();
+  const int c_lo = s_c[0], c_hi = s_c[1], nrows = c_hi - c_lo + 1;
+  auto row_m = [&](int n, int c) -> float {  // max of row (c, u) for head n; -inf if no such row
+    if (cta_range_start(c, a.n_ctas, T) == cta_range_start(c + 1, a.n_ctas, T)) return -INFINITY;
+    return a.rows[((int64_t)(c + u) * 8 + n) * (DH + 2)];
+  };
+  // pass 1: warp n -> global max and sum of head n
+  if (warp < a.grp) {
+    float M = -INFINITY;
+    for (int i = lane; i < nrows; i += 32) M = fmaxf(M, row_m(warp, c_lo + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    float L = 0.f;
+    if (M != -INFINITY)
+      for (int i = lane; i < nrows; i += 32) {
+        const float mw = row_m(warp, c_lo + i);
+        if (mw != -INFINITY)
+          L += a.rows[((int64_t)(c_lo + i + u) * 8 + warp) * (DH + 2) + 1] * exp2f(mw - M);
+      }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (lane == 0) { s_M[warp] = M; s_L[warp] = L; }
+  }
+  __syncthreads();
+  // pass 2: weights per chunk of rows, then threads over (head, dim)
+  float o_acc[(8 * DH + 255) / 256];
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) o_acc[q] = 0.f;
+  for (int c0 = 0; c0 < nrows; c0 += kChunk) {
+    const int nc = min(kChunk, nrows - c0);
+    for (int i = threadIdx.x; i < a.grp * nc; i += blockDim.x) {
+      const int n = i / nc, ci = i - n * nc;
+      const float mw = row_m(n, c_lo + c0 + ci);
+      s_w[n][ci] = (mw == -INFINITY || s_M[n] == -INFINITY) ? 0.f : exp2f(mw - s_M[n]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+      const int i = threadIdx.x + q * 256;
+      const int n = i / DH, d = i - n * DH;
+      if (n < a.grp) {
+        float o = o_acc[q];
+        for (int ci = 0; ci < nc; ++ci) {
+          const float w = s_w[n][ci];
+          if (w != 0.f) o += w * a.rows[((int64_t)(c_lo + c0 + ci + u) * 8 + n) * (DH + 2) + 2 + d];
+        }
+        o_acc[q] = o;
       }
     }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+    const int i = threadIdx.x + q * 256;
+    const int n = i / DH, d = i - n * DH;
+    if (n >= a.grp) continue;
+    const float M = s_M[n], l = s_L[n], o = o_acc[q];
     const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
     if (p.out_partial != nullptr) {
       float* dst = p.out_partial + hq * (DH + 2);
@@ -703,10 +888,10 @@ int validate_tiers(const sphkv_tiers& t, int dh) {
   return 0;
 }
 
-template <int DH, typename VT>
-static int launch_decode(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
+template <int DH, typename VT, bool ROT, bool EXTRA>
+static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   static int configured_for = -1;
-  auto kern = decode_splitk_kernel<DH, VT>;
+  auto kern = decode_splitk_kernel<DH, VT, ROT, EXTRA>;
   if (configured_for < smem_bytes) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -718,6 +903,16 @@ static int launch_decode(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   }
   kern<<<a.n_ctas, kWarps * 32, smem_bytes, st>>>(a);
   return check_launch("decode_splitk_kernel");
+}
+
+template <int DH, typename VT>
+static int launch_decode(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
+  const bool rot = a.p.rope_table != nullptr;
+  const bool extra = a.p.logits_out != nullptr || a.p.page_ml != nullptr;
+  if (rot) return extra ? launch_decode_t<DH, VT, true, true>(a, smem_bytes, st)
+                        : launch_decode_t<DH, VT, true, false>(a, smem_bytes, st);
+  return extra ? launch_decode_t<DH, VT, false, true>(a, smem_bytes, st)
+               : launch_decode_t<DH, VT, false, false>(a, smem_bytes, st);
 }
 
 }  // namespace sphkv
@@ -775,9 +970,10 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   SPHKV_REQUIRE(p.radius_fmt == SPHKV_RADIUS_I8 || p.radius_fmt == SPHKV_RADIUS_F16, SPHKV_E_ARG,
                 "decode: radius_fmt=%d", p.radius_fmt);
   SPHKV_REQUIRE(((uintptr_t)p.v_pool & 15) == 0 && ((uintptr_t)p.k_pages & 3) == 0 &&
+                    ((uintptr_t)p.codebooks & 15) == 0 && (p.tiers.g_max & 3) == 0 &&
                     (p.rope_table == nullptr || ((uintptr_t)p.rope_table & 15) == 0) &&
                     ((uintptr_t)p.scratch & 255) == 0,
-                SPHKV_E_ALIGN, "decode: v_pool/rope_table need 16 B, k_pages 4 B, scratch 256 B");
+                SPHKV_E_ALIGN, "decode: v_pool/rope_table/codebooks need 16 B, k_pages 4 B, scratch 256 B");
   if (int rc = validate_tiers(p.tiers, p.dh)) return rc;
 
   DecodeArgs a;
@@ -793,15 +989,18 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   a.rows = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.scratch) +
                                     align_up((int64_t)(a.n_units + 1) * 4, 256));
   a.cb_smem_bytes = smem_cb_layout(p.tiers, p.dh, a.cb_smem_off);
-  const int ks = p.dh / 16;
-  const int smem_bytes = kWarps * kVStages * 16 * p.dh * 2 + a.cb_smem_bytes +
-                         kWarps * (16 * ks * 8 + 512 + kMetaRing * 32);
+  a.plan_in_kernel = a.n_units <= kMaxUnitsInKernelPlan ? 1 : 0;
+  const int smem_bytes = smem_v_bytes(p.dh) + a.cb_smem_bytes + smem_q_bytes(p.dh) +
+                         kWarps * smem_priv_bytes(p.dh) +
+                         (a.plan_in_kernel ? (a.n_units + 1) * 4 : 0);
   SPHKV_REQUIRE(smem_bytes <= 227 * 1024, SPHKV_E_LIMIT,
                 "decode: codebooks need %d B of shared memory (limit %d)", smem_bytes, 227 * 1024);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
-  plan_kernel<<<1, 1024, 0, st>>>(p.num_blocks, a.n_units, p.max_blocks, a.pfx);
-  if (int rc = check_launch("plan_kernel")) return rc;
+  if (!a.plan_in_kernel) {
+    plan_kernel<<<1, 1024, 0, st>>>(p.num_blocks, a.n_units, p.max_blocks, p.B, p.Hkv, a.pfx);
+    if (int rc = check_launch("plan_kernel")) return rc;
+  }
   int rc;
   if (p.dh == 128)
     rc = p.v_dtype == SPHKV_F16 ? launch_decode<128, __half>(a, smem_bytes, st)
@@ -811,9 +1010,9 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
                                 : launch_decode<64, __nv_bfloat16>(a, smem_bytes, st);
   if (rc) return rc;
   if (p.dh == 128)
-    merge_rows_kernel<128><<<a.n_units, 128, 0, st>>>(a);
+    merge_rows_kernel<128><<<a.n_units, 256, 0, st>>>(a);
   else
-    merge_rows_kernel<64><<<a.n_units, 128, 0, st>>>(a);
+    merge_rows_kernel<64><<<a.n_units, 256, 0, st>>>(a);
   return check_launch("merge_rows_kernel");
 }
 

@@ -51,8 +51,8 @@ def check_against_oracle(cache, cbs, Q, ctx, dh, q_dtype=torch.float32, out_dtyp
     want, want_logits = orc.decode_cache(qd.float().cpu(), cc, cos, sin, torch.float64)
     got = out.float().cpu()
     # outputs: max-abs <= 2e-3; a bf16 output may additionally be off by its own rounding
-    # (half an ulp, 2^-9 relative)
-    slack = want.float().abs() * 2.0 ** -9 if out_dtype == torch.bfloat16 else 0.0
+    # (half an ulp: at most 2^-8 relative)
+    slack = want.float().abs() * 2.0 ** -8 if out_dtype == torch.bfloat16 else 0.0
     d_out = ((got - want.float()).abs() - slack).max().item()
     assert d_out <= out_tol, d_out
     # logits: |delta| <= 1e-3 * max(|ref|, 0.1*|q||k_hat|/sqrt(dh)), per stored token
@@ -184,9 +184,21 @@ def test_decode_matches_reference_golden_c1():
             pos = torch.cat([torch.nonzero(ax[0, h] == specs[s].tier_id).flatten() for s in order])
             kn = Kx[0, pos, h].double().norm(dim=1)
             tol = 1e-3 * torch.maximum(ref_l.abs(), 0.1 * qn * kn[None, :] / dh ** 0.5)
-            worst = max(worst, ((g - ref_l).abs() / tol).max().item())
-            d = (out[0, h * grp:(h + 1) * grp].float().cpu() - ref_o).abs().max().item()
-            assert d <= 2e-3, (name, h, d)
+            ratio = ((g - ref_l).abs() / tol).max().item()
+            assert ratio <= 1.0, (name, h, ratio)
+            worst = max(worst, ratio)
+            # outputs: 2e-3 max-abs "in bf16" (plus half a bf16 ulp of the value), plus what a
+            # logit perturbation inside the tolerance above may move the softmax average by
+            # (first order: sum_i p_i tol_i |v_i - out|) -- the pages hold fp16 radii, the
+            # reference used fp32 ones
+            o = out[0, h * grp:(h + 1) * grp].float().cpu()
+            pr = torch.softmax(ref_l, 1)
+            Vr = Vx[0, pos, h].half().double()
+            Vr[-1] = Vx[0, pos[-1], h].double()      # the current token's V stays fp32 in the reference
+            spread = (Vr[None, :, :] - ref_o.double()[:, None, :]).abs()
+            bound = 2e-3 + ref_o.abs() * 2.0 ** -8 + torch.einsum("qn,qnd->qd", pr * tol, spread).float()
+            d = ((o - ref_o).abs() / bound).max().item()
+            assert d <= 1.0, (name, h, d)
         assert worst <= 1.0, (name, worst)
 
 
