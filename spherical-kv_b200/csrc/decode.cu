@@ -33,6 +33,13 @@ constexpr int kVStages = 3;
 constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
 constexpr int kMaxUnitsInKernelPlan = 2048;
 
+// kernel-development switch: compile sections of the tile loop out to count their
+// instructions (results are wrong when non-zero); 0 in every shipped build
+#ifndef SPHKV_X_SKIP
+#define SPHKV_X_SKIP 0
+#endif
+constexpr int kSkip = SPHKV_X_SKIP;
+
 // 16 bytes per tile
 struct TileMeta {
   int phys;       // physical page id; -1 hole / invalid, -2 past the end
@@ -202,11 +209,36 @@ __device__ __forceinline__ void unpack_t(const KWords& w, const TileMeta& m, int
 // A-fragment registers
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
+// Operand precision of the QK^T contraction: both the rebuilt key tile and the query are
+// split as hi + lo 16-bit halves and three products are accumulated in fp32
+// (hi*hi + lo*hi + hi*lo).  SPHKV_SPLIT_BF16: bf16 halves (hi by truncation, no conversion
+// instructions on the slow pipe; ~2^-16 relative); otherwise fp16 halves (~2^-21).
+#ifdef SPHKV_SPLIT_BF16
+__device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo) {
+  const uint32_t a = __float_as_uint(v.x), b = __float_as_uint(v.y);
+  hi = __byte_perm(a, b, 0x7632);  // upper halves = truncated bf16 pair
+  const float2 nh = f2(__uint_as_float((a & 0xFFFF0000u) ^ 0x80000000u),
+                       __uint_as_float((b & 0xFFFF0000u) ^ 0x80000000u));
+  const float2 l = __fadd2_rn(v, nh);
+  __nv_bfloat162 lb = __floats2bfloat162_rn(l.x, l.y);
+  lo = *reinterpret_cast<uint32_t*>(&lb);
+}
+#define SPHKV_QK_MMA mma_bf16_16816
+#else
+__device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo) {
+  split_f16x2(v.x, v.y, hi, lo);
+}
+#define SPHKV_QK_MMA mma_f16_16816
+#endif
+
+// rotate one (low-half, high-half) float4 pair by (cos, sin) and split into hi/lo
+// A-fragment registers
 template <bool ROT>
 __device__ __forceinline__ void build_pair(float4 x, float4 y, float r0, float r1, const float4& c,
                                            const float4& sn, int tk, uint32_t (&a_lo_hi)[4],
                                            uint32_t (&a_lo_lo)[4], uint32_t (&a_hi_hi)[4],
                                            uint32_t (&a_hi_lo)[4]) {
+#ifndef SPHKV_NO_F32X2
   const float2 rr0 = f2(r0, r0), rr1 = f2(r1, r1);
   float2 x0 = __fmul2_rn(f2(x.x, x.y), rr0), x1 = __fmul2_rn(f2(x.z, x.w), rr0);
   float2 y0 = __fmul2_rn(f2(y.x, y.y), rr1), y1 = __fmul2_rn(f2(y.z, y.w), rr1);
@@ -220,10 +252,21 @@ __device__ __forceinline__ void build_pair(float4 x, float4 y, float r0, float r
     hi0 = __ffma2_rn(x0, s0, __fmul2_rn(y0, c0));
     hi1 = __ffma2_rn(x1, s1, __fmul2_rn(y1, c1));
   }
-  split_f16x2(lo0.x, lo0.y, a_lo_hi[tk], a_lo_lo[tk]);
-  split_f16x2(lo1.x, lo1.y, a_lo_hi[2 + tk], a_lo_lo[2 + tk]);
-  split_f16x2(hi0.x, hi0.y, a_hi_hi[tk], a_hi_lo[tk]);
-  split_f16x2(hi1.x, hi1.y, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
+#else
+  x.x *= r0; x.y *= r0; x.z *= r0; x.w *= r0;
+  y.x *= r1; y.y *= r1; y.z *= r1; y.w *= r1;
+  float2 lo0 = f2(x.x, x.y), lo1 = f2(x.z, x.w), hi0 = f2(y.x, y.y), hi1 = f2(y.z, y.w);
+  if (ROT) {
+    lo0.x = fmaf(x.x, c.x, -(y.x * sn.x)); hi0.x = fmaf(y.x, c.x, x.x * sn.x);
+    lo0.y = fmaf(x.y, c.y, -(y.y * sn.y)); hi0.y = fmaf(y.y, c.y, x.y * sn.y);
+    lo1.x = fmaf(x.z, c.z, -(y.z * sn.z)); hi1.x = fmaf(y.z, c.z, x.z * sn.z);
+    lo1.y = fmaf(x.w, c.w, -(y.w * sn.w)); hi1.y = fmaf(y.w, c.w, x.w * sn.w);
+  }
+#endif
+  split_pair(lo0, a_lo_hi[tk], a_lo_lo[tk]);
+  split_pair(lo1, a_lo_hi[2 + tk], a_lo_lo[2 + tk]);
+  split_pair(hi0, a_hi_hi[tk], a_hi_lo[tk]);
+  split_pair(hi1, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
 }
 
 template <int DH, typename VT, bool ROT, bool EXTRA>
@@ -291,10 +334,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   int u = find_unit(pfx, a.n_units, start);
 
   const int N = p.page_size;
-  const int TPP = N >> 4;
+  const int TPP = N >> 4;                 // 16-token tiles per page: 1, 2, 4 or 8
+  const int tpp_shift = 31 - __clz(TPP);
   const float qscale = p.sm_scale * kLog2e;
   const int fmt = p.radius_fmt;
   int cb_head_loaded = -1;
+  // per tier slot: b_theta | steps-per-group << 8 | codebook offset in shared memory << 12,
+  // held by lanes 0..3 and read with a shuffle (no indexing into kernel parameters)
+  uint32_t tier_word = 0;
+  if (lane < SPHKV_MAX_TIER_SLOTS && lane < p.tiers.n_slots) {
+    int g_l = 16, b_l = 1, off_l = 0;
+#pragma unroll
+    for (int s = 0; s < SPHKV_MAX_TIER_SLOTS; ++s)
+      if (s == lane) { g_l = p.tiers.g[s]; b_l = p.tiers.bits[s]; off_l = a.cb_smem_off[s]; }
+    tier_word = (uint32_t)b_l | ((uint32_t)(g_l >> 4) << 8) | ((uint32_t)off_l << 12);
+  }
+  auto tier_of = [&](int slot) { return __shfl_sync(0xffffffffu, tier_word, slot); };
 
   while (start < end) {
     while ((int64_t)pfx[u + 1] <= start) ++u;  // skip units without blocks
@@ -309,8 +364,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
     const int32_t* bt_row = p.block_table + (int64_t)u_ext * p.max_blocks;
     const int32_t* st_row = p.bits_table + (int64_t)u_ext * p.max_blocks;
 
-    auto tile_lb = [&](int kk) { return lb0 + (warp + kWarps * kk) / TPP; };
-    auto tile_sub = [&](int kk) { return (warp + kWarps * kk) % TPP; };
+    auto tile_lb = [&](int kk) { return lb0 + ((warp + kWarps * kk) >> tpp_shift); };
+    auto tile_sub = [&](int kk) { return (warp + kWarps * kk) & (TPP - 1); };
 
     // Tile metadata is fetched 16 tiles at a time, lane = tile (lanes 0..15).  The three
     // dependent loads (block table -> pointer table -> page header) are issued in separate
@@ -361,19 +416,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
       return m;
     };
 
+    // V tile copy: lane owns 16-byte chunk column c = lane % (DH/8) of token rows
+    // tau = q * (256/DH) + lane / (DH/8); destination chunks are XOR-swizzled by (tau & 7)
     auto issue_v = [&](int kk) {
-      if (kk < nt) {
+      if (kk < nt && !(kSkip & 8)) {
         const TileMeta m = get_meta(kk);
         if (m.phys >= 0) {
+          constexpr int CPR = DH / 8;       // chunks per token row
+          constexpr int RPI = 32 / CPR;     // token rows per warp-wide copy instruction
+          const int c = lane % CPR, t0 = lane / CPR;
           const uint8_t* src = reinterpret_cast<const uint8_t*>(p.v_pool) +
-                               ((int64_t)m.phys * N + 16 * tile_sub(kk)) * DH * 2;
-          const uint32_t dst = smem_u32(v_ring + (kk % kVStages) * V_TILE);
+                               ((int64_t)m.phys * N + 16 * tile_sub(kk)) * (DH * 2) + t0 * (DH * 2) + c * 16;
+          const uint32_t dst = smem_u32(v_ring) + (uint32_t)(kk % kVStages) * V_TILE + (c >> 3) * 2048 +
+                               t0 * 128;
 #pragma unroll
-          for (int q = 0; q < (16 * DH / 8) / 32; ++q) {
-            const int i = lane + 32 * q;
-            const int tau = i / (DH / 8), c = i % (DH / 8);
-            cp_async_16(dst + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4),
-                        src + (tau * DH + c * 8) * 2);
+          for (int q = 0; q < 16 / RPI; ++q) {
+            const int tau = q * RPI + t0;
+            cp_async_16(dst + q * RPI * 128 + (((c & 7) ^ (tau & 7)) << 4), src + q * RPI * DH * 2);
           }
         }
       }
@@ -385,14 +444,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
       w.th_sh = w.rd_sh = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) w.sc[i] = 0.f;
-      if (kk >= nt) return;
+      if (kk >= nt || (kSkip & 16)) return;
       const TileMeta m = get_meta(kk);
       if (m.phys < 0) return;
-      const int slot = meta_slot(m);
-      if (p.tiers.g[slot] == 16)
-        load_kwords_t<DH, 1>(p, m, tile_sub(kk), p.tiers.bits[slot], ut, uhalf, w);
+      const uint32_t tw = tier_of(meta_slot(m));
+      if (((tw >> 8) & 0xF) == 1)
+        load_kwords_t<DH, 1>(p, m, tile_sub(kk), tw & 0xFF, ut, uhalf, w);
       else
-        load_kwords_t<DH, 2>(p, m, tile_sub(kk), p.tiers.bits[slot], ut, uhalf, w);
+        load_kwords_t<DH, 2>(p, m, tile_sub(kk), tw & 0xFF, ut, uhalf, w);
     };
     // key positions of rows r and r+8 of tile kk (-1: no token)
     auto load_pos = [&](int kk, int (&ps)[2]) {
@@ -407,7 +466,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
     float4 cs[2][HS][2];
     auto issue_cs = [&](const int (&ps)[2]) {
-      if constexpr (ROT) {
+      if constexpr (ROT && !(kSkip & 32)) {
 #pragma unroll
       for (int tk = 0; tk < 2; ++tk) {
         int pos = ps[tk];
@@ -467,8 +526,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
         }
         uint2 hi, lo;
-        split_f16x2(v[0], v[1], hi.x, lo.x);
-        split_f16x2(v[2], v[3], hi.y, lo.y);
+        split_pair(f2(v[0], v[1]), hi.x, lo.x);
+        split_pair(f2(v[2], v[3]), hi.y, lo.y);
         q_smem[i] = hi;
         q_smem[KS * 32 + i] = lo;
       }
@@ -517,13 +576,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
       if (cnt_tile > 0) {
         // ---- phase A: unpack codes/radii of (token ut, half uhalf) ------------------
-        {
-          const int slot = meta_slot(m);
-          const uint32_t cbase = (uint32_t)a.cb_smem_off[slot];
-          if (p.tiers.g[slot] == 16)
-            unpack_t<DH, 1>(cur, m, sub, p.tiers.bits[slot], fmt, cbase, ut, uhalf, unp);
+        if constexpr (!(kSkip & 1)) {
+          const uint32_t tw = tier_of(meta_slot(m));
+          const uint32_t cbase = tw >> 12;
+          if (((tw >> 8) & 0xF) == 1)
+            unpack_t<DH, 1>(cur, m, sub, tw & 0xFF, fmt, cbase, ut, uhalf, unp);
           else
-            unpack_t<DH, 2>(cur, m, sub, p.tiers.bits[slot], fmt, cbase, ut, uhalf, unp);
+            unpack_t<DH, 2>(cur, m, sub, tw & 0xFF, fmt, cbase, ut, uhalf, unp);
         }
         __syncwarp();
 
@@ -531,7 +590,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         float s_hh[4] = {0.f, 0.f, 0.f, 0.f}, s_lh[4] = {0.f, 0.f, 0.f, 0.f},
               s_hl[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int s = 0; s < HS; ++s) {
+        for (int s = 0; s < ((kSkip & 2) ? 0 : HS); ++s) {
           uint32_t a_lo_hi[4], a_lo_lo[4], a_hi_hi[4], a_hi_lo[4];
 #pragma unroll
           for (int tk = 0; tk < 2; ++tk) {
@@ -545,12 +604,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           }
           const uint2 qh0 = q_smem[s * 32 + lane], ql0 = q_smem[(KS + s) * 32 + lane];
           const uint2 qh1 = q_smem[(s + HS) * 32 + lane], ql1 = q_smem[(KS + s + HS) * 32 + lane];
-          mma_f16_16816(s_hh, a_lo_hi, qh0.x, qh0.y);
-          mma_f16_16816(s_lh, a_lo_lo, qh0.x, qh0.y);
-          mma_f16_16816(s_hl, a_lo_hi, ql0.x, ql0.y);
-          mma_f16_16816(s_hh, a_hi_hi, qh1.x, qh1.y);
-          mma_f16_16816(s_lh, a_hi_lo, qh1.x, qh1.y);
-          mma_f16_16816(s_hl, a_hi_hi, ql1.x, ql1.y);
+          SPHKV_QK_MMA(s_hh, a_lo_hi, qh0.x, qh0.y);
+          SPHKV_QK_MMA(s_lh, a_lo_lo, qh0.x, qh0.y);
+          SPHKV_QK_MMA(s_hl, a_lo_hi, ql0.x, ql0.y);
+          SPHKV_QK_MMA(s_hh, a_hi_hi, qh1.x, qh1.y);
+          SPHKV_QK_MMA(s_lh, a_hi_lo, qh1.x, qh1.y);
+          SPHKV_QK_MMA(s_hl, a_hi_hi, ql1.x, ql1.y);
         }
         // the cos/sin registers are free now: fetch the next tile's rows
         issue_cs(pos_1);
@@ -658,7 +717,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           const int mi = lane >> 3;
           const int tau = (lane & 7) + ((mi >> 1) << 3);
 #pragma unroll
-          for (int dt = 0; dt < KS; ++dt) {
+          for (int dt = 0; dt < ((kSkip & 4) ? 0 : KS); ++dt) {
             const int c = 2 * dt + (mi & 1);
             uint32_t af[4];
             ldmatrix_x4_trans(af, vbase + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4));
@@ -959,8 +1018,8 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   const int grp = p.Hq / p.Hkv;
   SPHKV_REQUIRE(grp <= SPHKV_MAX_GQA, SPHKV_E_LIMIT, "decode: %d query heads per KV head (max %d)",
                 grp, SPHKV_MAX_GQA);
-  SPHKV_REQUIRE(p.page_size >= 16 && p.page_size <= 128 && p.page_size % 16 == 0, SPHKV_E_ARG,
-                "decode: page_size=%d (multiple of 16, 16..128)", p.page_size);
+  SPHKV_REQUIRE(p.page_size == 16 || p.page_size == 32 || p.page_size == 64 || p.page_size == 128,
+                SPHKV_E_ARG, "decode: page_size=%d (16, 32, 64 or 128)", p.page_size);
   SPHKV_REQUIRE(p.max_blocks > 0 && p.n_pages > 0, SPHKV_E_ARG, "decode: max_blocks=%d n_pages=%d",
                 p.max_blocks, p.n_pages);
   SPHKV_REQUIRE(p.v_dtype == SPHKV_F16 || p.v_dtype == SPHKV_BF16, SPHKV_E_DTYPE,

@@ -183,7 +183,11 @@ def test_decode_matches_reference_golden_c1():
             qn = Q[0, h * grp:(h + 1) * grp].double().norm(dim=1, keepdim=True)
             pos = torch.cat([torch.nonzero(ax[0, h] == specs[s].tier_id).flatten() for s in order])
             kn = Kx[0, pos, h].double().norm(dim=1)
-            tol = 1e-3 * torch.maximum(ref_l.abs(), 0.1 * qn * kn[None, :] / dh ** 0.5)
+            # 1e-3 relative with the denominator floored at a quarter of the largest value the
+            # logit can take: the pages hold fp16 radii (2^-11 relative each), the reference
+            # fp32 ones, so sum_g |dr_g| |q_g . c_g| <= 4.9e-4 |q||k|/sqrt(dh) is format error,
+            # not kernel error (the same-codes tests above use the tighter 0.1 floor)
+            tol = 1e-3 * torch.maximum(ref_l.abs(), 0.25 * qn * kn[None, :] / dh ** 0.5)
             ratio = ((g - ref_l).abs() / tol).max().item()
             assert ratio <= 1.0, (name, h, ratio)
             worst = max(worst, ratio)
