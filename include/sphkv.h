@@ -149,6 +149,22 @@ typedef struct sphkv_decode_params {
 int64_t sphkv_decode_scratch_bytes(int32_t B, int32_t Hkv, int32_t dh, int32_t n_ctas);
 int sphkv_decode_paged(const sphkv_decode_params* p, void* stream);
 
+/* Has no counterpart in the reference.  Same operation, arguments and results as
+ * sphkv_decode_paged, for callers that cannot provide scratch memory and must not cause an
+ * allocation: a serving process that committed all of its HBM to the KV pools at start-up,
+ * or a plug-in inside one, gets nothing back from cudaMalloc.  p->scratch and
+ * p->scratch_bytes are ignored; the split-K scratch is a fixed array inside the library
+ * image (about 1.7 MB on every GPU that loads the library, for the life of the process).
+ * Limits: B * Hkv <= 256, dh <= 128, at most 160 CTAs (p->n_ctas, or the SM count when 0);
+ * anything larger returns SPHKV_E_LIMIT.  The call performs no cudaMalloc / cudaFree and
+ * uses no allocating library routine.  Its first call on a device looks the array's device
+ * address up (cudaGetSymbolAddress, that device current): make that call before any stream
+ * capture begins.  All calls on a device share the one array, which keeps whatever the last
+ * call left in it (the kernels overwrite every word they later read, nothing needs
+ * clearing): two calls whose kernels may overlap on the GPU -- different streams, or two
+ * host threads -- race on it and must be serialised by the caller. */
+int sphkv_decode_paged_static(const sphkv_decode_params* p, void* stream);
+
 /* Log-sum-exp combine of R partial sets, each f32 [n_rows][dh+2] = (max, sum, acc),
  * natural-log max.  Same math as sphkv_reduce_kernel (decode_kernel.cu:221-246) with a
  * plain division (no +1e-8); rows whose total sum is 0 produce zeros.  Used after the

@@ -68,6 +68,7 @@ SIGNATURES = {
     "sphkv_encode_pages": (C.c_int, [C.POINTER(EncodeParams), C.c_void_p]),
     "sphkv_decode_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "sphkv_decode_paged": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),
+    "sphkv_decode_paged_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),
     "sphkv_merge_partials": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                        C.c_int32, C.c_void_p]),
     "sphkv_pool_decode": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 10 + [C.c_float, C.c_int32,

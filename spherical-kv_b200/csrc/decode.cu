@@ -1085,3 +1085,65 @@ extern "C" int sphkv_merge_partials(const float* parts, int32_t R, int32_t n_row
       parts, R, n_rows, dh, out, out_dtype);
   return check_launch("merge_partials_kernel");
 }
+
+// ---- decode without any caller- or library-side allocation -------------------------------
+// Some hosts of this library cannot hand it scratch memory: an inference server that gave
+// its whole HBM budget to the KV pools at start-up has nothing left for cudaMalloc to
+// return, and a plug-in loaded into such a process has no allocator of its own to ask.  For
+// them the split-K scratch of the decode kernels lives in the library image.
+//
+// Limits (the array is sized for them; every GPU that loads the library carries it until
+// the process exits): B * Hkv <= 256 units, at most 160 CTAs, dh <= 128.
+#define SPHKV_STATIC_MAX_UNITS 256
+#define SPHKV_STATIC_MAX_CTAS 160
+#define SPHKV_STATIC_SCRATCH_BYTES \
+  (((SPHKV_STATIC_MAX_UNITS + 1) * 4 + 255) / 256 * 256 + \
+   (SPHKV_STATIC_MAX_CTAS + SPHKV_STATIC_MAX_UNITS) * 8 * (128 + 2) * 4)
+static __device__ __align__(256) unsigned char g_static_scratch[SPHKV_STATIC_SCRATCH_BYTES];
+
+// g_static_scratch names a host-side handle here, not a device address; the address a
+// kernel can use comes from cudaGetSymbolAddress, asked once per device with that device
+// current.
+static void* static_scratch_for_current_device(int* rc_out) {
+  static void* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("decode_static: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    *rc_out = e != cudaSuccess ? (int)e : SPHKV_E_LIMIT;
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      set_error("decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      *rc_out = e != cudaSuccess ? (int)e : SPHKV_E_ARG;
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  *rc_out = 0;
+  return cached[dev];
+}
+
+extern "C" int sphkv_decode_paged_static(const sphkv_decode_params* pp, void* stream) {
+  SPHKV_REQUIRE(pp != nullptr, SPHKV_E_ARG, "decode_static: params is NULL");
+  SPHKV_REQUIRE(pp->B > 0 && pp->Hkv > 0 && (int64_t)pp->B * pp->Hkv <= SPHKV_STATIC_MAX_UNITS,
+                SPHKV_E_LIMIT, "decode_static: B*Hkv=%lld exceeds the built-in scratch (max %d units)",
+                (long long)pp->B * pp->Hkv, SPHKV_STATIC_MAX_UNITS);
+  SPHKV_REQUIRE(pp->dh > 0 && pp->dh <= 128, SPHKV_E_LIMIT,
+                "decode_static: dh=%d exceeds the built-in scratch (max 128)", pp->dh);
+  const int n_ctas = resolve_ctas(pp->n_ctas);
+  SPHKV_REQUIRE(n_ctas > 0 && n_ctas <= SPHKV_STATIC_MAX_CTAS, SPHKV_E_LIMIT,
+                "decode_static: %d CTAs exceed the built-in scratch (max %d); pass n_ctas", n_ctas,
+                SPHKV_STATIC_MAX_CTAS);
+  int rc = 0;
+  void* scratch = static_scratch_for_current_device(&rc);
+  if (scratch == nullptr) return rc;
+  sphkv_decode_params q = *pp;
+  q.n_ctas = n_ctas;
+  q.scratch = scratch;
+  q.scratch_bytes = SPHKV_STATIC_SCRATCH_BYTES;
+  return sphkv_decode_paged(&q, stream);
+}
