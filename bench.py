@@ -161,6 +161,109 @@ def workload_config(args) -> dict:
             "sharding": "batch rows per GPU, no collective"}
 
 
+def run_side_workload(args) -> None:
+    """Secondary measurements (not the headline line): split-KV decode of one long sequence
+    over the ranks (BASELINE config 5) and encode / page-build throughput (config 4)."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = importlib.import_module("spherical-kv_b200")
+    Hq, Hkv, dh, N = CFG["Hq"], CFG["Hkv"], CFG["dh"], CFG["page_size"]
+    specs = pkg.REFERENCE_TIERS[:2]
+    tiers = pkg.TierSet(dh, specs)
+    gen = torch.Generator(device=dev).manual_seed(77)
+    scale = torch.exp(0.5 * torch.randn(dh, generator=gen, device=dev))
+
+    def ev_time(fn, steps):
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    if args.workload == "splitkv":
+        ctx = 131072 if args.ctx == 32768 else args.ctx
+        n_seq = 8  # distinct sequences cycled so that a step never finds its pages in L2
+        rope = pkg.rope_table(ctx + 8, dh, device=dev)
+        decs, qs = [], []
+        for i in range(n_seq):
+            assign = pkg.synth.make_tier_assign(1, Hkv, ctx, {1: 0.2, 2: 0.6}, seed=500 + i).to(dev)
+            lists = pkg.build_page_lists(assign, tiers, N, shuffle_seed=i)
+            K = (torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+            V = (torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+            cb = tiers.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs, seed=i)])
+            cache = pkg.encode_pages(K, V, lists, cb, tiers, v_dtype=torch.bfloat16)
+            decs.append(pkg.split_kv.SplitKVDecoder(pkg.split_kv.shard_cache(cache, rank, world), 1, Hq,
+                                                    out_dtype=torch.bfloat16))
+            qs.append((torch.randn(1, Hq, dh, generator=gen, device=dev) * scale).bfloat16())
+            if i == 0:
+                alg = algorithmic_bytes(lists, tiers, dh) - 1 * Hq * dh * 4 + Hq * dh * 4
+        def step():
+            for d, q in zip(decs, qs):
+                d.decode(q, rope)
+        for _ in range(args.warmup):
+            step()
+        ms = ev_time(step, args.steps) / n_seq
+        if rank == 0:
+            print(json.dumps({"metric": "splitkv_decode_us_per_step", "value": ms * 1e3, "unit": "us",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                              "higher_is_better": False, "scaling": "strong", "data": "synthetic",
+                              "config": {"workload": f"split-KV decode, B1 Hq32 Hkv8 dh128 ctx {ctx}, 20/60/20, "
+                                                     f"pages sharded contiguously over {world} GPU(s), all-gather + "
+                                                     f"log-sum-exp merge; {n_seq} sequences cycled (L2)"},
+                              "algorithmic_bytes_total": alg,
+                              "achieved_hbm_gbs_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
+    else:  # encode
+        ctx, layers = args.ctx, min(args.layers, 8)
+        assign1 = torch.full((1, Hkv, ctx), 1, dtype=torch.uint8, device=dev)
+        assign2 = torch.full((1, Hkv, ctx), 2, dtype=torch.uint8, device=dev)
+        l1 = pkg.build_page_lists(assign1, tiers, N)
+        l2 = pkg.build_page_lists(assign2, tiers, N)
+        Ks = [(torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale) for _ in range(layers)]
+        for Kt in Ks:   # 1 % of the channels are x20 outliers
+            Kt[..., torch.randperm(dh, generator=torch.Generator().manual_seed(3))[:max(1, dh // 100)].to(dev)] *= 20
+        cb = tiers.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs, seed=9)])
+        c1 = pkg.encode_pages(Ks[0], Ks[0], l1, cb, tiers, v_dtype=torch.bfloat16)
+        c2 = pkg.encode_pages(Ks[0], None, l2, cb, tiers, v_dtype=torch.bfloat16)
+        def step():
+            for Kt in Ks:   # every token-head is matched against both codebooks (64 + 16 centroids)
+                pkg.encode_pages(Kt, Kt, l1, cb, tiers, out=c1)
+                pkg.encode_pages(Kt, None, l2, cb, tiers, out=c2)
+        for _ in range(args.warmup):
+            step()
+        ms = ev_time(step, args.steps)
+        th = layers * ctx * Hkv
+        rd = th * dh * 4 * 3          # K read twice (once per tier), V once, fp32
+        wr = layers * (l1.pool_bytes + l2.pool_bytes + l1.n_pages * N * dh * 2)
+        if rank == 0:
+            print(json.dumps({"metric": "encode_token_heads_per_s", "value": th / (ms * 1e-3), "unit": "token-heads/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+                              "higher_is_better": True, "data": "synthetic",
+                              "config": {"workload": f"spherical encode + page build, {ctx} tokens x {layers} layers x "
+                                                     f"{Hkv} KV heads x dh {dh}, fp32 K with 1% x20 outlier channels, "
+                                                     f"tier-1 (C=64) and tier-2 (C=16) pages for every token"},
+                              "gmac_per_s": th * (dh // 16) * 16 * 80 / (ms * 1e-3) / 1e9,
+                              "hbm_gbs": (rd + wr) / (ms * 1e-3) / 1e9}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,12 +274,18 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=CFG["layers"])
     ap.add_argument("--ctx", type=int, default=CFG["ctx"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "splitkv", "encode"],
+                    help="decode: the headline line (default); splitkv: one 131072-token sequence "
+                         "split over the ranks; encode: prefill compression throughput")
     args = ap.parse_args()
     CFG["layers"], CFG["ctx"] = args.layers, args.ctx
     if args.impl == "reference":
         run_reference(args)
         return
     args.warmup = max(args.warmup, 3)
+    if args.workload != "decode":
+        run_side_workload(args)
+        return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

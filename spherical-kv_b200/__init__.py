@@ -11,6 +11,7 @@ from . import _lib, pages, synth  # noqa: F401
 from ._lib import SphKVError, RADIUS_F16, RADIUS_I8  # noqa: F401
 from .pages import (PagedCache, PageLists, REFERENCE_TIERS, TierSet, TierSpec,  # noqa: F401
                     build_page_lists, shard_block_lists)
+from . import split_kv  # noqa: F401
 from .ops import (decode_paged, decode_scratch, encode_pages, hf_inv_freq,  # noqa: F401
                   merge_partials, rope_table)
 
