@@ -76,13 +76,13 @@ int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh, const floa
  * page lists, and the V/position page writes of _build_per_head_pages
  * (spherical_kv_pipeline.py:1146-1228).
  *
- * Work is described per bundle: 64 token slots = 64/page_size pages that share one
- * (KV head, tier slot); page_size > 64 uses one page per bundle. */
+ * Work is described per bundle: 128 token slots = 128/page_size pages that share one
+ * (KV head, tier slot). */
 typedef struct sphkv_encode_params {
   const void* k_src;        /* [rows][Hkv][dh], k_dtype; pre-RoPE keys                */
   const void* v_src;        /* same indexing, v_src_dtype; may be NULL (skip V)       */
   const int32_t* src_index; /* [P][page_size] source row per page slot, -1 = empty    */
-  const int32_t* bundles;   /* [n_bundles][4] physical page ids, -1 = unused          */
+  const int32_t* bundles;   /* [n_bundles][8] physical page ids, -1 = unused          */
   const int32_t* page_head; /* [P] KV head of each page (codebook selector)           */
   const int32_t* page_slot; /* [P] tier slot of each page                             */
   const int32_t* ptable;    /* [P][3] (page_off, theta_off, radius_off) byte offsets,

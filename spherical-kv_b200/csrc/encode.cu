@@ -1,7 +1,8 @@
 // Spherical encode + page build.
 //
-// One CTA encodes a bundle of 64 token slots (64/page_size pages, or 64-token chunks of
-// one larger page) that share a (KV head, tier slot): warp = group, lane = token.  Per
+// One CTA encodes bundles of 128 token slots (128/page_size pages) that share a (KV head,
+// tier slot): warp = group, lane = four tokens (every centroid row read from shared memory
+// feeds four dot products).  Per
 // (token, group) the kernel computes the group radius and the nearest centroid, then the
 // CTA assembles each page image in shared memory in the reference byte layout
 //   [tier_id u8][count u8][fmt u8][5 x 0][G x f32 scale][LSB-first packed theta][radii]
@@ -59,232 +60,269 @@ __device__ __forceinline__ void load_group(const void* base, int dtype, int64_t 
   }
 }
 
+constexpr int kBundlesPerCta = 8;  // consecutive bundles one CTA walks (they mostly share a codebook)
+
 template <int GS>
 __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const EncodeArgs a) {
   const sphkv_encode_params& p = a.p;
   extern __shared__ __align__(16) uint8_t smem[];
   const int N = p.page_size, dh = p.dh;
-  const int TB = N > 64 ? N : 64;           // token slots per bundle
-  const int n_chunks = TB / 64;
-  const int ppb = N >= 64 ? 1 : 64 / N;     // pages per bundle
+  constexpr int TB = 128;                   // token slots per bundle
+  const int ppb = TB / N;                   // pages per bundle (page_size <= 128)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  const int32_t* bundle = p.bundles + 4 * (int64_t)blockIdx.x;
-  int first = -1;
-  for (int q = 0; q < ppb; ++q)
-    if (first < 0 && bundle[q] >= 0) first = bundle[q];
-  if (first < 0) return;
-  const int head = p.page_head[first], slot = p.page_slot[first];
-  if (p.tiers.g[slot] != GS) return;  // the launch for the other group size takes this bundle
-  const int bits = p.tiers.bits[slot], C = 1 << bits, G = dh / GS;
+  const int G = dh / GS, g_shift = 31 - __clz(G);
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
+  const int C_cap = p.tiers.C_max;
 
   float* cb_s = reinterpret_cast<float*>(smem);                       // [G][C][GS]
-  float* r_s = cb_s + G * C * GS;                                      // [TB][G]
-  float* scale_s = r_s + TB * G;                                       // [4][8]
-  int* count_s = reinterpret_cast<int*>(scale_s + 32);                 // [4]
-  uint8_t* th_s = reinterpret_cast<uint8_t*>(count_s + 4);             // [TB][G]
+  float* r_s = cb_s + G * C_cap * GS;                                  // [TB][G]
+  float* scale_s = r_s + TB * G;                                       // [8][8]
+  int* count_s = reinterpret_cast<int*>(scale_s + 64);                 // [8]
+  int* page_s = count_s + 8;                                           // [8]
+  uint8_t* th_s = reinterpret_cast<uint8_t*>(page_s + 8);              // [TB][G]
   uint8_t* img = th_s + TB * G;                                        // page images, 16-aligned
   img = reinterpret_cast<uint8_t*>(((uintptr_t)img + 15) & ~(uintptr_t)15);
-  const int img_stride = ((8 + 4 * G + (N * G * bits + 7) / 8 + N * G * rb) + 15) & ~15;
 
-  // ---- codebook of (head, slot) -> shared memory ---------------------------------------
-  {
-    const float* src =
-        p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
-                          p.tiers.g_max;
-    const int total = G * C * GS;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-      const int d = i % GS, c = (i / GS) % C, gam = i / (GS * C);
-      cb_s[i] = src[((int64_t)gam * p.tiers.C_max + c) * p.tiers.g_max + d];
+  int loaded_key = -1;
+  const int b_first = blockIdx.x * kBundlesPerCta;
+  const int b_last = min(p.n_bundles, b_first + kBundlesPerCta);
+  for (int bi = b_first; bi < b_last; ++bi) {
+    const int32_t* bundle = p.bundles + 8 * (int64_t)bi;
+    __syncthreads();  // previous bundle is done with shared memory
+    // ---- pages of the bundle and their valid-token counts (valid slots form a prefix) ------
+    {  // 8 warps, up to 8 pages
+      int page = -1, cnt = 0;
+      if (warp < ppb) page = bundle[warp];
+      if (page >= 0) {
+        const int32_t* si = p.src_index + (int64_t)page * N;
+        for (int t0 = 0; t0 < N; t0 += 32) {
+          const bool ok = (t0 + lane < N) && si[t0 + lane] >= 0;
+          cnt += __popc(__ballot_sync(0xffffffffu, ok));
+        }
+      }
+      if (lane == 0) { count_s[warp] = cnt; page_s[warp] = page; }
     }
-  }
-  // ---- valid-token count per page (valid slots form a prefix) -----------------------------
-  if (threadIdx.x < 4) {
-    int cnt = 0;
-    if (threadIdx.x < ppb && bundle[threadIdx.x] >= 0) {
-      const int32_t* si = p.src_index + (int64_t)bundle[threadIdx.x] * N;
-      while (cnt < N && si[cnt] >= 0) ++cnt;
-    }
-    count_s[threadIdx.x] = cnt;
-  }
-  __syncthreads();
+    __syncthreads();
+    int first = -1;
+    for (int q = 0; q < ppb; ++q)
+      if (first < 0 && page_s[q] >= 0) first = page_s[q];
+    if (first < 0) continue;
+    const int head = p.page_head[first], slot = p.page_slot[first];
+    if (p.tiers.g[slot] != GS) continue;  // the launch for the other group size takes this bundle
+    const int bits = p.tiers.bits[slot], C = 1 << bits;
+    const int img_stride = ((8 + 4 * G + (N * G * bits + 7) / 8 + N * G * rb) + 15) & ~15;
 
-  // ---- radius + nearest centroid: warp = group, lane = token slot (two per thread) -------
-  if (warp < G) {
-    const float* cbg = cb_s + warp * C * GS;
-    for (int ch = 0; ch < n_chunks; ++ch) {
-      float k0[GS], k1[GS];
-      int tok[2];
-      bool have[2];
+    // ---- codebook of (head, slot) -> shared memory, 128-bit copies ---------------------------
+    if (head * p.tiers.n_slots + slot != loaded_key) {
+      const float4* src = reinterpret_cast<const float4*>(
+          p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
+                            p.tiers.g_max);
+      float4* dst = reinterpret_cast<float4*>(cb_s);
+      constexpr int Q4 = GS / 4;
+      const int total = (G << bits) * Q4;
+      const int row_stride4 = p.tiers.g_max >> 2;
+      for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int q4 = i % Q4, row = i / Q4;
+        const int c = row & (C - 1), gam = row >> bits;
+        dst[i] = __ldg(src + ((int64_t)gam * p.tiers.C_max + c) * row_stride4 + q4);
+      }
+      loaded_key = head * p.tiers.n_slots + slot;
+      __syncthreads();
+    }
+
+    // ---- radius + nearest centroid: warp = group, lane = token slots lane + 32 h, h < 4 ----
+    if (warp < G) {
+      const float* cbg = cb_s + (warp << bits) * GS;
+      float k[4][GS];
+      bool have[4];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int ts = ch * 64 + lane + 32 * h;  // token slot in bundle
-        const int q = N >= 64 ? 0 : ts / N, tin = N >= 64 ? ts : ts % N;
-        tok[h] = ts;
-        const int page = bundle[q];
+      for (int h = 0; h < 4; ++h) {
+        const int ts = lane + 32 * h;  // token slot in bundle
+        const int q = ts / N, tin = ts - q * N;
+        const int page = page_s[q];
         int64_t row = -1;
         if (page >= 0) row = p.src_index[(int64_t)page * N + tin];
         have[h] = row >= 0;
-        float (&kk)[GS] = h ? k1 : k0;
         if (have[h]) {
           load_group<GS>(p.k_src, p.k_dtype,
-                         row * p.k_row_stride + (int64_t)head * p.k_head_stride + warp * GS, kk);
+                         row * p.k_row_stride + (int64_t)head * p.k_head_stride + warp * GS, k[h]);
         } else {
 #pragma unroll
-          for (int i = 0; i < GS; ++i) kk[i] = 0.f;
+          for (int i = 0; i < GS; ++i) k[h][i] = 0.f;
         }
       }
-      float n0 = 0.f, n1 = 0.f;
+      float nsq[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int d = 0; d < GS; ++d) {
-        n0 = __fmaf_rn(k0[d], k0[d], n0);
-        n1 = __fmaf_rn(k1[d], k1[d], n1);
-      }
-      float best0 = -INFINITY, best1 = -INFINITY;
-      int code0 = 0, code1 = 0;
+      for (int d = 0; d < GS; ++d)
+#pragma unroll
+        for (int h = 0; h < 4; ++h) nsq[h] = __fmaf_rn(k[h][d], k[h][d], nsq[h]);
+      float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      int code[4] = {0, 0, 0, 0};
       for (int c = 0; c < C; ++c) {
         const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
-        float s0 = 0.f, s1 = 0.f;
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < GS / 4; ++i) {
           const float4 v = row[i];
-          s0 = __fmaf_rn(k0[4 * i], v.x, s0); s1 = __fmaf_rn(k1[4 * i], v.x, s1);
-          s0 = __fmaf_rn(k0[4 * i + 1], v.y, s0); s1 = __fmaf_rn(k1[4 * i + 1], v.y, s1);
-          s0 = __fmaf_rn(k0[4 * i + 2], v.z, s0); s1 = __fmaf_rn(k1[4 * i + 2], v.z, s1);
-          s0 = __fmaf_rn(k0[4 * i + 3], v.w, s0); s1 = __fmaf_rn(k1[4 * i + 3], v.w, s1);
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            sacc[h] = __fmaf_rn(k[h][4 * i], v.x, sacc[h]);
+            sacc[h] = __fmaf_rn(k[h][4 * i + 1], v.y, sacc[h]);
+            sacc[h] = __fmaf_rn(k[h][4 * i + 2], v.z, sacc[h]);
+            sacc[h] = __fmaf_rn(k[h][4 * i + 3], v.w, sacc[h]);
+          }
         }
-        if (s0 > best0) { best0 = s0; code0 = c; }
-        if (s1 > best1) { best1 = s1; code1 = c; }
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          if (sacc[h] > best[h]) { best[h] = sacc[h]; code[h] = c; }
       }
-      r_s[tok[0] * G + warp] = have[0] ? __fsqrt_rn(n0) : 0.f;
-      r_s[tok[1] * G + warp] = have[1] ? __fsqrt_rn(n1) : 0.f;
-      th_s[tok[0] * G + warp] = (uint8_t)code0;
-      th_s[tok[1] * G + warp] = (uint8_t)code1;
-    }
-  }
-  __syncthreads();
-
-  // ---- per-page, per-group scale = max radius over the page's tokens ----------------------
-  if (warp < ppb) {
-    const int cnt = count_s[warp];
-    const int tbase = N >= 64 ? 0 : warp * N;
-    const int gq = lane & 7, tq = lane >> 3;
-    float mx = 0.f;
-    if (gq < G)
-      for (int t = tq; t < cnt; t += 4) mx = fmaxf(mx, r_s[(tbase + t) * G + gq]);
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-    if (lane < 8) scale_s[warp * 8 + lane] = mx;
-  }
-  __syncthreads();
-
-  // ---- page images: header, scales, packed theta words ---------------------------------------
-  for (int q = 0; q < ppb; ++q) {
-    const int cnt = count_s[q];
-    if (cnt == 0) continue;
-    uint8_t* im = img + q * img_stride;
-    const int tbase = N >= 64 ? 0 : q * N;
-    const int hdr = 8 + 4 * G;
-    const int nvals = cnt * G;
-    const int th_bytes = (nvals * bits + 7) >> 3;
-    const int th_words = (th_bytes + 3) >> 2;
-    if (threadIdx.x < 2) {
-      uint32_t w = 0;
-      if (threadIdx.x == 0)
-        w = (uint32_t)(p.tiers.tier_id[slot] & 0xFF) | ((uint32_t)(cnt & 0xFF) << 8) |
-            ((uint32_t)(p.radius_fmt & 0xFF) << 16);
-      reinterpret_cast<uint32_t*>(im)[threadIdx.x] = w;
-    }
-    if (threadIdx.x < G) reinterpret_cast<float*>(im + 8)[threadIdx.x] = scale_s[q * 8 + threadIdx.x];
-    for (int w = threadIdx.x; w < th_words; w += blockDim.x) {
-      const int bit0 = w * 32;
-      int i = bit0 / bits;  // first value overlapping this word
-      uint32_t acc = 0;
-      for (; i < nvals && i * bits < bit0 + 32; ++i) {
-        const uint32_t v = th_s[tbase * G + i];
-        const int sh = i * bits - bit0;
-        acc |= sh >= 0 ? (v << sh) : (v >> (-sh));
-      }
-      reinterpret_cast<uint32_t*>(im + hdr)[w] = acc;
-    }
-  }
-  __syncthreads();
-  // ---- radii (may overlay the zero tail of the last theta word) ----------------------------
-  for (int q = 0; q < ppb; ++q) {
-    const int cnt = count_s[q];
-    if (cnt == 0) continue;
-    uint8_t* im = img + q * img_stride;
-    const int tbase = N >= 64 ? 0 : q * N;
-    const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
-    for (int i = threadIdx.x; i < cnt * G; i += blockDim.x) {
-      const int gq = i % G;
-      const float rr = r_s[tbase * G + i];
-      if (rb == 1) {
-        const float safe = fmaxf(scale_s[q * 8 + gq], 1e-8f);
-        float qv = rintf(__fmul_rn(__fdiv_rn(rr, safe), 127.0f));
-        qv = fminf(fmaxf(qv, -127.f), 127.f);
-        im[roff + i] = (uint8_t)(int8_t)(int)qv;
-      } else {
-        // stage the half's bit pattern as a 32-bit word over the radius slot (same thread
-        // read it above); the bytes are laid into the page image after the barrier
-        unsigned short hv;
-        asm volatile("cvt.rn.f16.f32 %0, %1;" : "=h"(hv) : "f"(rr));
-        reinterpret_cast<uint32_t*>(r_s)[tbase * G + i] = (uint32_t)hv;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const int ts = lane + 32 * h;
+        r_s[ts * G + warp] = have[h] ? __fsqrt_rn(nsq[h]) : 0.f;
+        th_s[ts * G + warp] = (uint8_t)code[h];
       }
     }
-  }
-  if (rb == 2) {
     __syncthreads();
+
+    // ---- per-page, per-group scale = max radius over the page's tokens ----------------------
+    if (warp < ppb) {
+      const int cnt = count_s[warp];
+      const int tbase = warp * N;
+      const int gq = lane & 7, tq = lane >> 3;
+      float mx = 0.f;
+      if (gq < G)
+        for (int t = tq; t < cnt; t += 4) mx = fmaxf(mx, r_s[(tbase + t) * G + gq]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      if (lane < 8) scale_s[warp * 8 + lane] = mx;
+    }
+    __syncthreads();
+
+    // ---- page images: header, scales, packed theta words ---------------------------------------
     for (int q = 0; q < ppb; ++q) {
       const int cnt = count_s[q];
       if (cnt == 0) continue;
       uint8_t* im = img + q * img_stride;
-      const int tbase = N >= 64 ? 0 : q * N;
-      const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
-      const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_s + tbase * G);
-      for (int b = threadIdx.x; b < 2 * cnt * G; b += blockDim.x)
-        im[roff + b] = hb[(b >> 1) * 4 + (b & 1)];
+      const int tbase = q * N;
+      const int hdr = 8 + 4 * G;
+      const int nvals = cnt * G;
+      const int th_bytes = (nvals * bits + 7) >> 3;
+      const int th_words = (th_bytes + 3) >> 2;
+      if (threadIdx.x < 2) {
+        uint32_t w = 0;
+        if (threadIdx.x == 0)
+          w = (uint32_t)(p.tiers.tier_id[slot] & 0xFF) | ((uint32_t)(cnt & 0xFF) << 8) |
+              ((uint32_t)(p.radius_fmt & 0xFF) << 16);
+        reinterpret_cast<uint32_t*>(im)[threadIdx.x] = w;
+      }
+      if (threadIdx.x < G) reinterpret_cast<float*>(im + 8)[threadIdx.x] = scale_s[q * 8 + threadIdx.x];
+      for (int w = threadIdx.x; w < th_words; w += blockDim.x) {
+        const int bit0 = w * 32;
+        int i = bit0 / bits;  // first value overlapping this word
+        uint32_t acc = 0;
+        for (; i < nvals && i * bits < bit0 + 32; ++i) {
+          const uint32_t v = th_s[tbase * G + i];
+          const int sh = i * bits - bit0;
+          acc |= sh >= 0 ? (v << sh) : (v >> (-sh));
+        }
+        reinterpret_cast<uint32_t*>(im + hdr)[w] = acc;
+      }
     }
-  }
-  __syncthreads();
-  // ---- copy page images out -------------------------------------------------------------------
-  for (int q = 0; q < ppb; ++q) {
-    const int cnt = count_s[q];
-    if (cnt == 0) continue;
-    const int page = bundle[q];
-    const uint8_t* im = img + q * img_stride;
-    const int bytes = 8 + 4 * G + ((cnt * G * bits + 7) >> 3) + cnt * G * rb;
-    uint8_t* dst = p.k_pages + p.ptable[3 * (int64_t)page];
-    const int words = bytes >> 2;
-    for (int w = threadIdx.x; w < words; w += blockDim.x)
-      reinterpret_cast<uint32_t*>(dst)[w] = reinterpret_cast<const uint32_t*>(im)[w];
-    if ((int)threadIdx.x < (bytes & 3)) dst[words * 4 + threadIdx.x] = im[words * 4 + threadIdx.x];
-  }
-
-  // ---- dense V pages (16-bit), empty slots zero-filled ------------------------------------------
-  if (p.v_src != nullptr && p.v_pool != nullptr) {
-    const int per_row = dh / 2;  // element pairs per row
+    __syncthreads();
+    // ---- radii (may overlay the zero tail of the last theta word) ----------------------------
     for (int q = 0; q < ppb; ++q) {
-      const int page = bundle[q];
-      if (page < 0) continue;
-      for (int i = threadIdx.x; i < N * per_row; i += blockDim.x) {
-        const int t = i / per_row, d = (i - t * per_row) * 2;
-        const int64_t row = p.src_index[(int64_t)page * N + t];
-        float v0 = 0.f, v1 = 0.f;
-        if (row >= 0) {
-          const int64_t off = row * p.v_row_stride + (int64_t)head * p.v_head_stride + d;
-          v0 = load_as_float(p.v_src, p.v_src_dtype, off);
-          v1 = load_as_float(p.v_src, p.v_src_dtype, off + 1);
-        }
-        uint32_t packed;
-        if (p.v_pool_dtype == SPHKV_F16) {
-          packed = pack_f16x2(v0, v1);
+      const int cnt = count_s[q];
+      if (cnt == 0) continue;
+      uint8_t* im = img + q * img_stride;
+      const int tbase = q * N;
+      const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
+      for (int i = threadIdx.x; i < cnt * G; i += blockDim.x) {
+        const int gq = i & (G - 1);
+        const float rr = r_s[tbase * G + i];
+        if (rb == 1) {
+          const float safe = fmaxf(scale_s[q * 8 + gq], 1e-8f);
+          float qv = rintf(__fmul_rn(__fdiv_rn(rr, safe), 127.0f));
+          qv = fminf(fmaxf(qv, -127.f), 127.f);
+          im[roff + i] = (uint8_t)(int8_t)(int)qv;
         } else {
-          __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-          packed = *reinterpret_cast<uint32_t*>(&h);
+          // stage the half's bit pattern as a 32-bit word over the radius slot (same thread
+          // read it above); the bytes are laid into the page image after the barrier
+          unsigned short hv;
+          asm volatile("cvt.rn.f16.f32 %0, %1;" : "=h"(hv) : "f"(rr));
+          reinterpret_cast<uint32_t*>(r_s)[tbase * G + i] = (uint32_t)hv;
         }
-        reinterpret_cast<uint32_t*>(p.v_pool)[(((int64_t)page * N + t) * dh + d) >> 1] = packed;
+      }
+    }
+    if (rb == 2) {
+      __syncthreads();
+      for (int q = 0; q < ppb; ++q) {
+        const int cnt = count_s[q];
+        if (cnt == 0) continue;
+        uint8_t* im = img + q * img_stride;
+        const int tbase = q * N;
+        const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
+        const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_s + tbase * G);
+        for (int b = threadIdx.x; b < 2 * cnt * G; b += blockDim.x)
+          im[roff + b] = hb[(b >> 1) * 4 + (b & 1)];
+      }
+    }
+    __syncthreads();
+    // ---- copy page images out -------------------------------------------------------------------
+    for (int q = 0; q < ppb; ++q) {
+      const int cnt = count_s[q];
+      if (cnt == 0) continue;
+      const int page = page_s[q];
+      const uint8_t* im = img + q * img_stride;
+      const int bytes = 8 + 4 * G + ((cnt * G * bits + 7) >> 3) + cnt * G * rb;
+      uint8_t* dst = p.k_pages + p.ptable[3 * (int64_t)page];
+      const int words = bytes >> 2;
+      for (int w = threadIdx.x; w < words; w += blockDim.x)
+        reinterpret_cast<uint32_t*>(dst)[w] = reinterpret_cast<const uint32_t*>(im)[w];
+      if ((int)threadIdx.x < (bytes & 3)) dst[words * 4 + threadIdx.x] = im[words * 4 + threadIdx.x];
+    }
+
+    // ---- dense V pages (16-bit), empty slots zero-filled: 8 elements per thread-step --------
+    if (p.v_src != nullptr && p.v_pool != nullptr) {
+      const int per_row = dh >> 3;  // 16-byte output chunks per row
+      for (int q = 0; q < ppb; ++q) {
+        const int page = page_s[q];
+        if (page < 0) continue;
+        for (int i = threadIdx.x; i < N * per_row; i += blockDim.x) {
+          const int t = i / per_row, d = (i - t * per_row) * 8;
+          const int64_t row = p.src_index[(int64_t)page * N + t];
+          uint4 o = make_uint4(0u, 0u, 0u, 0u);
+          if (row >= 0) {
+            const int64_t off = row * p.v_row_stride + (int64_t)head * p.v_head_stride + d;
+            if (p.v_src_dtype == p.v_pool_dtype &&
+                (((uintptr_t)p.v_src + off * 2) & 15) == 0) {
+              o = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.v_src) + off));
+            } else {
+              float v[8];
+              if (p.v_src_dtype == SPHKV_F32 && (((uintptr_t)p.v_src + off * 4) & 15) == 0) {
+                const float4 a0 = ldg_stream_f4(reinterpret_cast<const float*>(p.v_src) + off);
+                const float4 a1 = ldg_stream_f4(reinterpret_cast<const float*>(p.v_src) + off + 4);
+                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
+                v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = load_as_float(p.v_src, p.v_src_dtype, off + e);
+              }
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (p.v_pool_dtype == SPHKV_F16) {
+                  w[e] = pack_f16x2(v[2 * e], v[2 * e + 1]);
+                } else {
+                  __nv_bfloat162 hb2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                  w[e] = *reinterpret_cast<uint32_t*>(&hb2);
+                }
+              }
+              o = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+          reinterpret_cast<uint4*>(p.v_pool)[(((int64_t)page * N + t) * dh + d) >> 3] = o;
+        }
       }
     }
   }
@@ -347,16 +385,18 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
                 SPHKV_E_DTYPE, "encode: v_pool_dtype=%d", p.v_pool_dtype);
   SPHKV_REQUIRE(p.radius_fmt == SPHKV_RADIUS_I8 || p.radius_fmt == SPHKV_RADIUS_F16, SPHKV_E_ARG,
                 "encode: radius_fmt=%d", p.radius_fmt);
-  SPHKV_REQUIRE(((uintptr_t)p.k_pages & 3) == 0 && ((uintptr_t)p.v_pool & 3) == 0, SPHKV_E_ALIGN,
-                "encode: k_pages / v_pool need 4 B alignment");
+  SPHKV_REQUIRE(((uintptr_t)p.k_pages & 3) == 0, SPHKV_E_ALIGN, "encode: k_pages needs 4 B alignment");
   if (int rc = validate_tiers(p.tiers, p.dh)) return rc;
-  // shared memory: largest codebook + staging + page images
-  const int N = p.page_size, TB = N > 64 ? N : 64, ppb = N >= 64 ? 1 : 64 / N;
+  SPHKV_REQUIRE(((uintptr_t)p.codebooks & 15) == 0 && (p.tiers.g_max & 3) == 0 &&
+                    ((uintptr_t)p.v_pool & 15) == 0,
+                SPHKV_E_ALIGN, "encode: codebooks / v_pool need 16 B alignment, g_max a multiple of 4");
+  // shared memory: codebook of the widest tier + staging + page images
+  const int N = p.page_size, TB = 128, ppb = TB / N;
   int smem_bytes = 0;
   for (int s = 0; s < p.tiers.n_slots; ++s) {
-    const int G = p.dh / p.tiers.g[s], C = 1 << p.tiers.bits[s];
+    const int G = p.dh / p.tiers.g[s];
     const int img = ((8 + 4 * G + (N * G * p.tiers.bits[s] + 7) / 8 + N * G * 2) + 15) & ~15;
-    const int need = G * C * p.tiers.g[s] * 4 + TB * G * 4 + 32 * 4 + 16 + TB * G + 16 + ppb * img;
+    const int need = p.dh * p.tiers.C_max * 4 + TB * G * 4 + 64 * 4 + 64 + TB * G + 16 + ppb * img;
     smem_bytes = need > smem_bytes ? need : smem_bytes;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -379,11 +419,11 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
   bool any16 = false, any32 = false;
   for (int s = 0; s < p.tiers.n_slots; ++s) (p.tiers.g[s] == 16 ? any16 : any32) = true;
   if (any16) {
-    encode_bundle_kernel<16><<<p.n_bundles, kEncThreads, smem_bytes, st>>>(a);
+    encode_bundle_kernel<16><<<(p.n_bundles + kBundlesPerCta - 1) / kBundlesPerCta, kEncThreads, smem_bytes, st>>>(a);
     if (int rc = check_launch("encode_bundle_kernel<16>")) return rc;
   }
   if (any32) {
-    encode_bundle_kernel<32><<<p.n_bundles, kEncThreads, smem_bytes, st>>>(a);
+    encode_bundle_kernel<32><<<(p.n_bundles + kBundlesPerCta - 1) / kBundlesPerCta, kEncThreads, smem_bytes, st>>>(a);
     if (int rc = check_launch("encode_bundle_kernel<32>")) return rc;
   }
   return 0;

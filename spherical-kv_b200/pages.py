@@ -115,7 +115,7 @@ class PageLists:
     block_table: torch.Tensor    # i32 [B*Hkv, max_blocks]
     bits_table: torch.Tensor     # i32 [B*Hkv, max_blocks]
     num_blocks: torch.Tensor     # i32 [B*Hkv]
-    bundles: torch.Tensor        # i32 [n_bundles, 4]
+    bundles: torch.Tensor        # i32 [n_bundles, 8]: 128 token slots = 128/page_size pages
     pool_bytes: int
     B: int
     Hkv: int
@@ -141,7 +141,7 @@ def build_page_lists(tier_assign: torch.Tensor, tiers: TierSet, page_size: int,
     N = page_size
     U = B * Hkv
     rb = 2 if radius_fmt == _lib.RADIUS_F16 else 1
-    ppb = 1 if N >= 64 else 64 // N
+    ppb = 128 // N
     ta = tier_assign.reshape(U, T)
 
     per_slot = []  # (unit, rank, t) per retained token, page counts per unit
@@ -213,7 +213,7 @@ def build_page_lists(tier_assign: torch.Tensor, tiers: TierSet, page_size: int,
         # bundles: ppb consecutive pages of one run
         nb_u = (npg + ppb - 1) // ppb
         b_base = torch.cumsum(nb_u, 0) - nb_u
-        bun = torch.full((int(nb_u.sum().item()), 4), -1, dtype=torch.int32, device=dev)
+        bun = torch.full((int(nb_u.sum().item()), 8), -1, dtype=torch.int32, device=dev)
         bun[b_base[unit_of_page] + pin // ppb, pin % ppb] = ph.to(torch.int32)
         bundle_rows.append(bun)
 

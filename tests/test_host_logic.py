@@ -99,7 +99,7 @@ def test_page_lists_partition_tokens(page_size, shuffle):
     bun = L.bundles
     ids = bun[bun >= 0]
     assert sorted(ids.tolist()) == list(range(L.n_pages))
-    ppb = 1 if N >= 64 else 64 // N
+    ppb = 128 // N
     assert (bun[:, ppb:] == -1).all()
     for row in bun.tolist():
         live = [x for x in row if x >= 0]
