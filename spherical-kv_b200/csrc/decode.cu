@@ -29,7 +29,7 @@
 namespace sphkv {
 
 constexpr int kWarps = 12;
-constexpr int kVStages = 3;
+constexpr int kVStages = 2;
 constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
 constexpr int kMaxUnitsInKernelPlan = 2048;
 
@@ -197,7 +197,7 @@ __device__ __forceinline__ void unpack_t(const KWords& w, const TileMeta& m, int
     const uint32_t row = (((uint32_t)(gam0 + i) << bits) + code) * SPG;
 #pragma unroll
     for (int s2 = 0; s2 < SPG; ++s2)
-      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * 64u, __float_as_uint(rad));
+      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * 128u, __float_as_uint(rad));
   }
   uint2* dst = unp + ut * KS + gam0 * SPG;  // 16-byte aligned: KS and NG*SPG are even
 #pragma unroll
@@ -285,6 +285,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
   uint8_t* v_ring = smem + warp * V_WARP;
   uint8_t* cb_smem = smem + smem_v_bytes(DH);
+  const uint8_t* cb_lane = cb_smem + j * 16 + (r & 1) * 64;  // this lane's chunk of its copy
   uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [2][KS][32]
   uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) + warp * smem_priv_bytes(DH);
   uint2* unp = reinterpret_cast<uint2*>(warp_priv);                       // [16][KS]
@@ -503,10 +504,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           const float4* sp = reinterpret_cast<const float4*>(
               src + ((int64_t)gam * tg.C_max + c) * tg.g_max + sub2 * 16);
           const float4 v0 = __ldg(sp), v1 = __ldg(sp + 1), v2 = __ldg(sp + 2), v3 = __ldg(sp + 3);
-          dst[row * 4 + 0] = make_float4(v0.x, v0.y, v2.x, v2.y);
-          dst[row * 4 + 1] = make_float4(v0.z, v0.w, v2.z, v2.w);
-          dst[row * 4 + 2] = make_float4(v1.x, v1.y, v3.x, v3.y);
-          dst[row * 4 + 3] = make_float4(v1.z, v1.w, v3.z, v3.w);
+          // each 64-byte sub-row is stored twice, at bytes 0 and 64 of a 128-byte slot: even
+          // tokens read the first copy, odd tokens the second, so the two tokens served by one
+          // shared-memory wavefront never meet in a bank
+          const float4 w0 = make_float4(v0.x, v0.y, v2.x, v2.y), w1 = make_float4(v0.z, v0.w, v2.z, v2.w);
+          const float4 w2 = make_float4(v1.x, v1.y, v3.x, v3.y), w3 = make_float4(v1.z, v1.w, v3.z, v3.w);
+          dst[row * 8 + 0] = w0; dst[row * 8 + 1] = w1; dst[row * 8 + 2] = w2; dst[row * 8 + 3] = w3;
+          dst[row * 8 + 4] = w0; dst[row * 8 + 5] = w1; dst[row * 8 + 6] = w2; dst[row * 8 + 7] = w3;
         }
       }
       cb_head_loaded = hkv;
@@ -597,8 +601,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             const int tau = r + 8 * tk;
             const uint2 e0 = unp[tau * KS + s];
             const uint2 e1 = unp[tau * KS + s + HS];
-            const float4 x = *reinterpret_cast<const float4*>(cb_smem + e0.x + j * 16);
-            const float4 y = *reinterpret_cast<const float4*>(cb_smem + e1.x + j * 16);
+            const float4 x = *reinterpret_cast<const float4*>(cb_lane + e0.x);
+            const float4 y = *reinterpret_cast<const float4*>(cb_lane + e1.x);
             build_pair<ROT>(x, y, __uint_as_float(e0.y), __uint_as_float(e1.y), cs[tk][s][0],
                             cs[tk][s][1], tk, a_lo_hi, a_lo_lo, a_hi_hi, a_hi_lo);
           }
@@ -925,7 +929,7 @@ static int smem_cb_layout(const sphkv_tiers& t, int dh, int* offs) {
   int off = 0;
   for (int s = 0; s < t.n_slots; ++s) {
     offs[s] = off;
-    off += dh * (1 << t.bits[s]) * 4;
+    off += dh * (1 << t.bits[s]) * 4 * 2;  // every sub-row twice
   }
   return off;
 }
