@@ -33,6 +33,8 @@ import torch  # noqa: E402
 
 CFG = dict(B=8, Hq=32, Hkv=8, dh=128, ctx=32768, layers=32, page_size=16)
 METRIC, UNIT = "decode_attn_us_per_layer_step", "us"
+# measured DRAM bytes / algorithmic bytes of the decode kernel (profiles/decode_splitk_ctx16k_ncu.txt)
+DRAM_TRAFFIC_RATIO = 1.097
 
 
 def algorithmic_bytes(lists, tiers, dh: int) -> float:
@@ -408,7 +410,9 @@ def main() -> None:
                     "d2h_bytes_per_step": out_host.numel() * 2},
             "gpu_launches": 2 * NL * args.steps * 2,  # decode + merge kernel per layer-step, graph leg and e2e leg
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "frac": achieved / peak, "traffic": alg_bytes * DRAM_TRAFFIC_RATIO, "peak_source": peak_src,
+                         "traffic_source": "ncu dram__bytes_read+write of one decode launch on a ctx-16384 case "
+                                           "(294.7 MB for 268.7 MB algorithmic), scaled by token-heads",
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "note": "duration = one layer-step (decode + merge kernels) from CUDA "
                                  "events over the timed region; frac_of_8TBs = %.3f" % (achieved / 8000.0)},
