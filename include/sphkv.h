@@ -90,6 +90,10 @@ typedef struct sphkv_encode_params {
   const float* codebooks;   /* see sphkv_tiers                                        */
   uint8_t* k_pages;         /* out: byte pool                                         */
   void* v_pool;             /* out: [P][page_size][dh], v_pool_dtype (F16 or BF16)    */
+  void* scratch;            /* optional, sphkv_encode_scratch_bytes() bytes, 16-aligned:
+                               with it the search and the page assembly run as two
+                               launches (faster); NULL = one fused launch              */
+  int64_t scratch_bytes;
   int64_t k_row_stride;     /* elements between consecutive source rows               */
   int64_t k_head_stride;    /* elements between consecutive heads of a row            */
   int64_t v_row_stride, v_head_stride;
@@ -99,6 +103,7 @@ typedef struct sphkv_encode_params {
   sphkv_tiers tiers;
 } sphkv_encode_params;
 
+int64_t sphkv_encode_scratch_bytes(int32_t n_pages, int32_t page_size, int32_t dh);
 int sphkv_encode_pages(const sphkv_encode_params* p, void* stream);
 
 /* ---- Decode ----------------------------------------------------------------------

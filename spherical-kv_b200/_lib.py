@@ -31,7 +31,7 @@ class EncodeParams(C.Structure):
         ("k_src", C.c_void_p), ("v_src", C.c_void_p), ("src_index", C.c_void_p),
         ("bundles", C.c_void_p), ("page_head", C.c_void_p), ("page_slot", C.c_void_p),
         ("ptable", C.c_void_p), ("codebooks", C.c_void_p), ("k_pages", C.c_void_p),
-        ("v_pool", C.c_void_p),
+        ("v_pool", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
         ("k_row_stride", C.c_int64), ("k_head_stride", C.c_int64),
         ("v_row_stride", C.c_int64), ("v_head_stride", C.c_int64),
         ("n_bundles", C.c_int32), ("n_pages", C.c_int32), ("page_size", C.c_int32),
@@ -66,6 +66,7 @@ SIGNATURES = {
     "sphkv_struct_size": (C.c_int, [C.c_int]),
     "sphkv_rope_table_build": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "sphkv_encode_pages": (C.c_int, [C.POINTER(EncodeParams), C.c_void_p]),
+    "sphkv_encode_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "sphkv_decode_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "sphkv_decode_paged": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),
     "sphkv_decode_paged_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),

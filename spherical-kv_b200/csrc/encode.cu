@@ -22,6 +22,7 @@ namespace sphkv {
 
 struct EncodeArgs {
   sphkv_encode_params p;
+  int bundles_per_cta;
 };
 
 constexpr int kEncThreads = 256;
@@ -60,9 +61,13 @@ __device__ __forceinline__ void load_group(const void* base, int dtype, int64_t 
   }
 }
 
-constexpr int kBundlesPerCta = 8;  // consecutive bundles one CTA walks (they mostly share a codebook)
+constexpr int kMaxBundlesPerCta = 8;  // consecutive bundles one CTA walks (they mostly share a codebook)
 
-template <int GS>
+// PHASE 0: everything in one kernel (no scratch needed).  PHASE 1: radius + nearest-centroid
+// search only, results to the scratch arrays r[(page*N + slot) * (dh/16) + group] (f32) and
+// theta[...] (u8).  PHASE 2: page assembly + V pages from those arrays.  Splitting lets the
+// FMA-bound search run without the barriers and small dependent loads of the page bookkeeping.
+template <int GS, int PHASE>
 __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const EncodeArgs a) {
   const sphkv_encode_params& p = a.p;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -71,8 +76,12 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   const int ppb = TB / N;                   // pages per bundle (page_size <= 128)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = dh / GS, g_shift = 31 - __clz(G);
+  const int n_shift = 31 - __clz(N);  // page_size is a power of two
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-  const int C_cap = p.tiers.C_max;
+  const int C_cap = PHASE == 2 ? 0 : p.tiers.C_max;
+  const int GST = dh >> 4;  // group stride of the scratch arrays
+  float* scr_r = reinterpret_cast<float*>(p.scratch);
+  uint8_t* scr_t = reinterpret_cast<uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
 
   float* cb_s = reinterpret_cast<float*>(smem);                       // [G][C][GS]
   float* r_s = cb_s + G * C_cap * GS;                                  // [TB][G]
@@ -84,8 +93,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   img = reinterpret_cast<uint8_t*>(((uintptr_t)img + 15) & ~(uintptr_t)15);
 
   int loaded_key = -1;
-  const int b_first = blockIdx.x * kBundlesPerCta;
-  const int b_last = min(p.n_bundles, b_first + kBundlesPerCta);
+  const int b_first = blockIdx.x * a.bundles_per_cta;
+  const int b_last = min(p.n_bundles, b_first + a.bundles_per_cta);
   for (int bi = b_first; bi < b_last; ++bi) {
     const int32_t* bundle = p.bundles + 8 * (int64_t)bi;
     __syncthreads();  // previous bundle is done with shared memory
@@ -113,7 +122,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     const int img_stride = ((8 + 4 * G + (N * G * bits + 7) / 8 + N * G * rb) + 15) & ~15;
 
     // ---- codebook of (head, slot) -> shared memory, 128-bit copies ---------------------------
-    if (head * p.tiers.n_slots + slot != loaded_key) {
+    if (PHASE != 2 && head * p.tiers.n_slots + slot != loaded_key) {
       const float4* src = reinterpret_cast<const float4*>(
           p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
                             p.tiers.g_max);
@@ -131,14 +140,14 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     }
 
     // ---- radius + nearest centroid: warp = group, lane = token slots lane + 32 h, h < 4 ----
-    if (warp < G) {
+    if (PHASE != 2 && warp < G) {
       const float* cbg = cb_s + (warp << bits) * GS;
       float k[4][GS];
       bool have[4];
 #pragma unroll
       for (int h = 0; h < 4; ++h) {
         const int ts = lane + 32 * h;  // token slot in bundle
-        const int q = ts / N, tin = ts - q * N;
+        const int q = ts >> n_shift, tin = ts & (N - 1);
         const int page = page_s[q];
         int64_t row = -1;
         if (page >= 0) row = p.src_index[(int64_t)page * N + tin];
@@ -179,8 +188,36 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
 #pragma unroll
       for (int h = 0; h < 4; ++h) {
         const int ts = lane + 32 * h;
-        r_s[ts * G + warp] = have[h] ? __fsqrt_rn(nsq[h]) : 0.f;
-        th_s[ts * G + warp] = (uint8_t)code[h];
+        const float rv = have[h] ? __fsqrt_rn(nsq[h]) : 0.f;
+        if (PHASE == 1) {
+          const int q = ts >> n_shift, tin = ts & (N - 1);
+          const int page = page_s[q];
+          if (page >= 0) {
+            const int64_t si = ((int64_t)page * N + tin) * GST + warp;
+            scr_r[si] = rv;
+            scr_t[si] = (uint8_t)code[h];
+          }
+        } else {
+          r_s[ts * G + warp] = rv;
+          th_s[ts * G + warp] = (uint8_t)code[h];
+        }
+      }
+    }
+    if (PHASE == 1) continue;  // the assembly launch takes it from here
+    if (PHASE == 2) {
+      for (int i = threadIdx.x; i < TB * G; i += blockDim.x) {
+        const int ts = i >> g_shift, gq = i & (G - 1);
+        const int q = ts >> n_shift, tin = ts & (N - 1);
+        const int page = page_s[q];
+        float rv = 0.f;
+        uint8_t tv = 0;
+        if (page >= 0) {
+          const int64_t si = ((int64_t)page * N + tin) * GST + gq;
+          rv = scr_r[si];
+          tv = scr_t[si];
+        }
+        r_s[i] = rv;
+        th_s[i] = tv;
       }
     }
     __syncthreads();
@@ -367,6 +404,24 @@ extern "C" int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh,
   return check_launch("rope_table_kernel");
 }
 
+template <int GS>
+static int launch_encode(const EncodeArgs& a, bool split, int smem_bytes, cudaStream_t st) {
+  const int grid = (a.p.n_bundles + a.bundles_per_cta - 1) / a.bundles_per_cta;
+  if (split) {
+    encode_bundle_kernel<GS, 1><<<grid, kEncThreads, smem_bytes, st>>>(a);
+    if (int rc = check_launch("encode_bundle_kernel<search>")) return rc;
+    encode_bundle_kernel<GS, 2><<<grid, kEncThreads, smem_bytes, st>>>(a);
+    return check_launch("encode_bundle_kernel<assemble>");
+  }
+  encode_bundle_kernel<GS, 0><<<grid, kEncThreads, smem_bytes, st>>>(a);
+  return check_launch("encode_bundle_kernel<fused>");
+}
+
+extern "C" int64_t sphkv_encode_scratch_bytes(int32_t n_pages, int32_t page_size, int32_t dh) {
+  if (n_pages <= 0 || page_size <= 0 || dh <= 0) return SPHKV_E_ARG;
+  return ((int64_t)n_pages * page_size * (dh / 16) * 5 + 15) / 16 * 16;
+}
+
 extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
   SPHKV_REQUIRE(pp != nullptr, SPHKV_E_ARG, "encode: params is NULL");
   const sphkv_encode_params& p = *pp;
@@ -402,13 +457,30 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   EncodeArgs a;
   a.p = p;
+  {  // long runs per CTA amortise the codebook staging, but only once every SM has several CTAs
+    static int sms = 0;
+    if (sms <= 0) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 148;
+    }
+    int bpc = p.n_bundles / (sms * 8);
+    a.bundles_per_cta = bpc < 1 ? 1 : (bpc > kMaxBundlesPerCta ? kMaxBundlesPerCta : bpc);
+  }
+  const int64_t scratch_need = sphkv_encode_scratch_bytes(p.n_pages, p.page_size, p.dh);
+  const bool split = p.scratch != nullptr && p.scratch_bytes >= scratch_need &&
+                     ((uintptr_t)p.scratch & 15) == 0;
   static int configured = 0;
   if (configured < smem_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(encode_bundle_kernel<16>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(encode_bundle_kernel<32>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    cudaError_t e = cudaSuccess;
+    auto set = [&](const void* f) {
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    };
+    set((const void*)encode_bundle_kernel<16, 0>); set((const void*)encode_bundle_kernel<16, 1>);
+    set((const void*)encode_bundle_kernel<16, 2>); set((const void*)encode_bundle_kernel<32, 0>);
+    set((const void*)encode_bundle_kernel<32, 1>); set((const void*)encode_bundle_kernel<32, 2>);
     if (e != cudaSuccess) {
       set_error("encode: cudaFuncSetAttribute(%d B): %s", smem_bytes, cudaGetErrorString(e));
       return (int)e;
@@ -419,12 +491,10 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
   bool any16 = false, any32 = false;
   for (int s = 0; s < p.tiers.n_slots; ++s) (p.tiers.g[s] == 16 ? any16 : any32) = true;
   if (any16) {
-    encode_bundle_kernel<16><<<(p.n_bundles + kBundlesPerCta - 1) / kBundlesPerCta, kEncThreads, smem_bytes, st>>>(a);
-    if (int rc = check_launch("encode_bundle_kernel<16>")) return rc;
+    if (int rc = launch_encode<16>(a, split, smem_bytes, st)) return rc;
   }
   if (any32) {
-    encode_bundle_kernel<32><<<(p.n_bundles + kBundlesPerCta - 1) / kBundlesPerCta, kEncThreads, smem_bytes, st>>>(a);
-    if (int rc = check_launch("encode_bundle_kernel<32>")) return rc;
+    if (int rc = launch_encode<32>(a, split, smem_bytes, st)) return rc;
   }
   return 0;
 }

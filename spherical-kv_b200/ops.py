@@ -52,7 +52,7 @@ def rope_table(max_pos: int, dh: int, base: float = 500000.0, device="cuda",
 def encode_pages(k_src: torch.Tensor, v_src: Optional[torch.Tensor], lists: PageLists,
                  codebooks: torch.Tensor, tiers: TierSet, radius_fmt: int = _lib.RADIUS_I8,
                  v_dtype: torch.dtype = torch.float16,
-                 out: Optional[PagedCache] = None) -> PagedCache:
+                 out: Optional[PagedCache] = None, use_scratch: bool = True) -> PagedCache:
     """Encodes [rows, Hkv, dh] pre-RoPE keys (and values) into the pages `lists` describes.
 
     Mirrors _encode_keys_with_codebooks + build_page_from_codes over whole page lists
@@ -75,6 +75,13 @@ def encode_pages(k_src: torch.Tensor, v_src: Optional[torch.Tensor], lists: Page
     p.page_head, p.page_slot = lists.page_head.data_ptr(), lists.page_slot.data_ptr()
     p.ptable, p.codebooks = lists.ptable.data_ptr(), codebooks.data_ptr()
     p.k_pages, p.v_pool = out.k_pages.data_ptr(), out.v_pool.data_ptr()
+    if use_scratch:
+        need = lib.sphkv_encode_scratch_bytes(lists.n_pages, lists.page_size, dh)
+        scr = out.extra.get("encode_scratch")
+        if scr is None or scr.numel() < need:
+            scr = torch.empty(need, dtype=torch.uint8, device=dev)
+            out.extra["encode_scratch"] = scr
+        p.scratch, p.scratch_bytes = scr.data_ptr(), scr.numel()
     p.k_row_stride, p.k_head_stride = k_src.stride(0), k_src.stride(1)
     if v_src is not None:
         p.v_row_stride, p.v_head_stride = v_src.stride(0), v_src.stride(1)

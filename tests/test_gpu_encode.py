@@ -30,7 +30,7 @@ def oracle_pages(K, assign, lists, tiers, cbs, radius_fmt):
 
 
 def run_case(B, Hkv, dh, T, page_size, specs, fractions, radius_fmt=0, k_dtype=torch.float32,
-             v_dtype=torch.float16, shuffle=5, per_head=True, seed=0, outliers=0.0):
+             v_dtype=torch.float16, shuffle=5, per_head=True, seed=0, outliers=0.0, use_scratch=True):
     dev = torch.device("cuda:0")
     tiers = pkg.TierSet(dh, specs)
     K, V, _, _ = synth.make_kvq(B, Hkv, Hkv, dh, T, seed=seed, outlier_frac=outliers)
@@ -42,7 +42,7 @@ def run_case(B, Hkv, dh, T, page_size, specs, fractions, radius_fmt=0, k_dtype=t
                           for k, v in lists.__dict__.items()})
     cache = pkg.encode_pages(K.reshape(B * T, Hkv, dh).to(dev), V.reshape(B * T, Hkv, dh).to(dev), dl,
                              tiers.pack_codebooks(cbs).to(dev), tiers, radius_fmt=radius_fmt,
-                             v_dtype=v_dtype)
+                             v_dtype=v_dtype, use_scratch=use_scratch)
     torch.cuda.synchronize()
     got = cache.k_pages.cpu().numpy()
     want = oracle_pages(K.float(), assign, lists, tiers, cbs, radius_fmt)
@@ -69,6 +69,12 @@ def test_encode_bit_exact_tiers_1_2(dh, page_size):
 def test_encode_bit_exact_all_tiers_ragged(page_size):
     """three tiers incl. g=32, ragged per-head lists, partial last pages, outlier channels"""
     run_case(1, 3, 128, 523, page_size, pkg.REFERENCE_TIERS, {1: 0.2, 2: 0.5, 3: 0.2}, outliers=0.01)
+
+
+def test_encode_fused_single_launch_path():
+    """without scratch the search and the page assembly run as one launch: same bytes"""
+    run_case(2, 2, 128, 500, 16, pkg.REFERENCE_TIERS, {1: 0.3, 2: 0.4, 3: 0.2}, use_scratch=False)
+    run_case(1, 2, 64, 300, 32, pkg.REFERENCE_TIERS[:2], {1: 0.5, 2: 0.4}, use_scratch=False)
 
 
 def test_encode_single_token_pages_and_empty_units():
