@@ -220,7 +220,30 @@ def run_side_workload(args) -> None:
                 d.decode(q, rope)
         for _ in range(args.warmup):
             step()
-        ms = ev_time(step, args.steps) / n_seq
+        # one CUDA graph for the whole step (decode kernels, all-gathers, merges): the exchange is
+        # latency-bound, so launch gaps matter; fall back to plain launches if capture is refused
+        graphed = False
+        try:
+            if world > 1:
+                # ranks must issue identical collective sequences; a capture that fails on one
+                # rank only would leave the others waiting, so multi-rank runs use plain launches
+                raise RuntimeError("multi-rank: plain launches")
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            run = g.replay
+            graphed = True
+        except Exception as exc:  # noqa: BLE001
+            run = step
+        for _ in range(args.warmup):
+            run()
+        ms = ev_time(run, args.steps) / n_seq
         if rank == 0:
             print(json.dumps({"metric": "splitkv_decode_us_per_step", "value": ms * 1e3, "unit": "us",
                               "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -228,7 +251,7 @@ def run_side_workload(args) -> None:
                               "config": {"workload": f"split-KV decode, B1 Hq32 Hkv8 dh128 ctx {ctx}, 20/60/20, "
                                                      f"pages sharded contiguously over {world} GPU(s), all-gather + "
                                                      f"log-sum-exp merge; {n_seq} sequences cycled (L2)"},
-                              "algorithmic_bytes_total": alg,
+                              "cuda_graph": graphed, "algorithmic_bytes_total": alg,
                               "achieved_hbm_gbs_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
     else:  # encode
         ctx, layers = args.ctx, min(args.layers, 8)
