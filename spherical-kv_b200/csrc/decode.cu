@@ -269,7 +269,9 @@ __device__ __forceinline__ void build_pair(float4 x, float4 y, float r0, float r
   split_pair(hi1, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
 }
 
-template <int DH, typename VT, bool ROT, bool EXTRA>
+// PACK (<= 4 query heads per KV head): the 8 mma columns carry [q_hi heads 0..3 | q_lo heads
+// 0..3] (one product fewer per step) and later [P_hi | P_lo] (one product per V tile).
+template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
 __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const DecodeArgs a) {
   constexpr int KS = DH / 16;  // 16-dim steps over the head dim
   constexpr int HS = KS / 2;   // steps in one rotary half
@@ -521,8 +523,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
     auto stage_q = [&]() {
       for (int i = threadIdx.x; i < KS * 32; i += blockDim.x) {
         const int s = i >> 5, ln = i & 31, n = ln >> 2, jj = ln & 3;
-        const bool real = n < a.grp;
-        const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * DH;
+        const int head = PACK ? (n & 3) : n;
+        const bool real = head < a.grp;
+        const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + head) * DH;
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -532,8 +535,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         uint2 hi, lo;
         split_pair(f2(v[0], v[1]), hi.x, lo.x);
         split_pair(f2(v[2], v[3]), hi.y, lo.y);
-        q_smem[i] = hi;
-        q_smem[KS * 32 + i] = lo;
+        if (PACK) {
+          q_smem[i] = n < 4 ? hi : lo;   // columns 0..3: hi halves, 4..7: lo halves
+        } else {
+          q_smem[i] = hi;
+          q_smem[KS * 32 + i] = lo;
+        }
       }
     };
 
@@ -606,14 +613,22 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             build_pair<ROT>(x, y, __uint_as_float(e0.y), __uint_as_float(e1.y), cs[tk][s][0],
                             cs[tk][s][1], tk, a_lo_hi, a_lo_lo, a_hi_hi, a_hi_lo);
           }
-          const uint2 qh0 = q_smem[s * 32 + lane], ql0 = q_smem[(KS + s) * 32 + lane];
-          const uint2 qh1 = q_smem[(s + HS) * 32 + lane], ql1 = q_smem[(KS + s + HS) * 32 + lane];
-          SPHKV_QK_MMA(s_hh, a_lo_hi, qh0.x, qh0.y);
-          SPHKV_QK_MMA(s_lh, a_lo_lo, qh0.x, qh0.y);
-          SPHKV_QK_MMA(s_hl, a_lo_hi, ql0.x, ql0.y);
-          SPHKV_QK_MMA(s_hh, a_hi_hi, qh1.x, qh1.y);
-          SPHKV_QK_MMA(s_lh, a_hi_lo, qh1.x, qh1.y);
-          SPHKV_QK_MMA(s_hl, a_hi_hi, ql1.x, ql1.y);
+          if (PACK) {
+            const uint2 q0 = q_smem[s * 32 + lane], q1 = q_smem[(s + HS) * 32 + lane];
+            SPHKV_QK_MMA(s_hh, a_lo_hi, q0.x, q0.y);
+            SPHKV_QK_MMA(s_lh, a_lo_lo, q0.x, q0.y);
+            SPHKV_QK_MMA(s_hh, a_hi_hi, q1.x, q1.y);
+            SPHKV_QK_MMA(s_lh, a_hi_lo, q1.x, q1.y);
+          } else {
+            const uint2 qh0 = q_smem[s * 32 + lane], ql0 = q_smem[(KS + s) * 32 + lane];
+            const uint2 qh1 = q_smem[(s + HS) * 32 + lane], ql1 = q_smem[(KS + s + HS) * 32 + lane];
+            SPHKV_QK_MMA(s_hh, a_lo_hi, qh0.x, qh0.y);
+            SPHKV_QK_MMA(s_lh, a_lo_lo, qh0.x, qh0.y);
+            SPHKV_QK_MMA(s_hl, a_lo_hi, ql0.x, ql0.y);
+            SPHKV_QK_MMA(s_hh, a_hi_hi, qh1.x, qh1.y);
+            SPHKV_QK_MMA(s_lh, a_hi_lo, qh1.x, qh1.y);
+            SPHKV_QK_MMA(s_hl, a_hi_hi, ql1.x, ql1.y);
+          }
         }
         // the cos/sin registers are free now: fetch the next tile's rows
         issue_cs(pos_1);
@@ -621,13 +636,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         // ---- online softmax over the 16 token rows, per head column ------------------
         float sv[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sv[e] = s_hh[e] + (s_lh[e] + s_hl[e]);
+        for (int e = 0; e < 4; ++e) {
+          sv[e] = s_hh[e] + (s_lh[e] + s_hl[e]);
+          // packed columns: head h's logit = column h (x q_hi) + column 4+h (x q_lo)
+          if (PACK) sv[e] += __shfl_xor_sync(0xffffffffu, sv[e], 2);
+        }
         if (EXTRA && p.logits_out != nullptr) {
           const int lb = tile_lb(k);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int n = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
-            if (n < a.grp && tok < cnt_tile)
+            if (n < a.grp && tok < cnt_tile && (!PACK || j < 2))
               p.logits_out[(((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + lb) * N +
                            16 * sub + tok] = sv[e] * kLn2;
           }
@@ -676,7 +695,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
               const int n = 2 * j + c;
-              if (n < a.grp) {
+              if (n < a.grp && (!PACK || j < 2)) {
                 float* dst = p.page_ml + (((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks +
                                           tile_lb(k)) * 2;
                 const float tm = tmax[c];
@@ -695,13 +714,21 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int head = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
+            uint16_t hbits, lbits;
             if (kBf16) {
               const __nv_bfloat16 h = __float2bfloat16_rn(pv[e]);
-              const __nv_bfloat16 l = __float2bfloat16_rn(pv[e] - __bfloat162float(h));
-              ph[head * 16 + tok] = __bfloat16_as_ushort(h);
-              pl[head * 16 + tok] = __bfloat16_as_ushort(l);
+              hbits = __bfloat16_as_ushort(h);
+              lbits = __bfloat16_as_ushort(__float2bfloat16_rn(pv[e] - __bfloat162float(h)));
             } else {
-              ph[head * 16 + tok] = __half_as_ushort(__float2half_rn(pv[e]));
+              hbits = __half_as_ushort(__float2half_rn(pv[e]));
+              lbits = 0;
+            }
+            if (PACK) {
+              // columns 0..3 hold P (hi half), columns 4..7 the lo half (zero for an fp16 V pool)
+              ph[head * 16 + tok] = j < 2 ? hbits : lbits;
+            } else {
+              ph[head * 16 + tok] = hbits;
+              if (kBf16) pl[head * 16 + tok] = lbits;
             }
           }
         }
@@ -712,7 +739,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           const uint32_t b0 = ph32[(r * 16 + 2 * j) >> 1];
           const uint32_t b1 = ph32[(r * 16 + 2 * j + 8) >> 1];
           uint32_t c0 = 0, c1 = 0;
-          if (kBf16) {
+          if (kBf16 && !PACK) {
             c0 = ph32[(8 * 16 + r * 16 + 2 * j) >> 1];
             c1 = ph32[(8 * 16 + r * 16 + 2 * j + 8) >> 1];
           }
@@ -727,7 +754,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             ldmatrix_x4_trans(af, vbase + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4));
             if (kBf16) {
               mma_bf16_16816(acc[dt], af, b0, b1);
-              mma_bf16_16816(acc[dt], af, c0, c1);
+              if (!PACK) mma_bf16_16816(acc[dt], af, c0, c1);
             } else {
               mma_f16_16816(acc[dt], af, b0, b1);
             }
@@ -787,7 +814,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             for (int w = 0; w < kWarps; ++w) {
               const float* wb = reinterpret_cast<const float*>(smem + w * V_WARP) + n * (DH + 2);
               const float mw = wb[0];
-              if (mw != -INFINITY) outv += wb[e] * fast_exp2(mw - M);
+              if (mw != -INFINITY) {
+                float val = wb[e];
+                if (PACK && e >= 2) val += wb[4 * (DH + 2) + e];  // the P_lo columns
+                outv += val * fast_exp2(mw - M);
+              }
             }
           }
         }
@@ -951,10 +982,10 @@ int validate_tiers(const sphkv_tiers& t, int dh) {
   return 0;
 }
 
-template <int DH, typename VT, bool ROT, bool EXTRA>
+template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
 static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   static int configured_for = -1;
-  auto kern = decode_splitk_kernel<DH, VT, ROT, EXTRA>;
+  auto kern = decode_splitk_kernel<DH, VT, ROT, EXTRA, PACK>;
   if (configured_for < smem_bytes) {
     cudaError_t e =
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -968,14 +999,20 @@ static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st)
   return check_launch("decode_splitk_kernel");
 }
 
+template <int DH, typename VT, bool ROT>
+static int launch_decode_r(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
+  const bool extra = a.p.logits_out != nullptr || a.p.page_ml != nullptr;
+  const bool pack = a.grp <= 4;
+  if (extra) return pack ? launch_decode_t<DH, VT, ROT, true, true>(a, smem_bytes, st)
+                         : launch_decode_t<DH, VT, ROT, true, false>(a, smem_bytes, st);
+  return pack ? launch_decode_t<DH, VT, ROT, false, true>(a, smem_bytes, st)
+              : launch_decode_t<DH, VT, ROT, false, false>(a, smem_bytes, st);
+}
+
 template <int DH, typename VT>
 static int launch_decode(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
-  const bool rot = a.p.rope_table != nullptr;
-  const bool extra = a.p.logits_out != nullptr || a.p.page_ml != nullptr;
-  if (rot) return extra ? launch_decode_t<DH, VT, true, true>(a, smem_bytes, st)
-                        : launch_decode_t<DH, VT, true, false>(a, smem_bytes, st);
-  return extra ? launch_decode_t<DH, VT, false, true>(a, smem_bytes, st)
-               : launch_decode_t<DH, VT, false, false>(a, smem_bytes, st);
+  return a.p.rope_table != nullptr ? launch_decode_r<DH, VT, true>(a, smem_bytes, st)
+                                   : launch_decode_r<DH, VT, false>(a, smem_bytes, st);
 }
 
 }  // namespace sphkv

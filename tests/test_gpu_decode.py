@@ -95,6 +95,16 @@ def test_decode_matches_oracle(dh, Hq, Hkv, page_size):
     check_against_oracle(cache, cbs, Q, ctx, dh)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(16, 2), (4, 2), (2, 2), (12, 2)])
+@pytest.mark.parametrize("v_dtype", [torch.float16, torch.bfloat16])
+def test_decode_query_group_sizes(Hq, Hkv, v_dtype):
+    """8, 2, 1 and 6 query heads per KV head (<= 4 uses the packed hi|lo mma columns)"""
+    ctx, dh = 640, 128
+    cache, cbs, K, V, Q, _ = build(2, Hq, Hkv, dh, ctx, 16, pkg.REFERENCE_TIERS[:2], {1: 0.4, 2: 0.5},
+                                   v_dtype=v_dtype, seed=31)
+    check_against_oracle(cache, cbs, Q, ctx, dh)
+
+
 def test_decode_three_tiers_bf16_io_and_v():
     ctx, dh = 1500, 128
     cache, cbs, K, V, Q, _ = build(2, 16, 4, dh, ctx, 16, pkg.REFERENCE_TIERS, {1: 0.2, 2: 0.4, 3: 0.2},
