@@ -356,6 +356,17 @@ def main() -> None:
     out_dev = torch.empty(NL, B, Hq, dh, dtype=torch.bfloat16, device=dev)
     out_host = torch.empty(NL, B, Hq, dh, dtype=torch.bfloat16).pin_memory()
 
+    # size-independent self-check at full size: the result must not depend on how the blocks are
+    # split over CTAs (148 vs 37 vs 5 CTAs walk very different tile sequences per warp)
+    ref_out = pkg.decode_paged(q_dev[0], caches[0], rope).float()
+    self_check = 0.0
+    for n_alt in (37, 5):
+        alt = pkg.PagedCache(tiers=caches[0].tiers, lists=caches[0].lists, codebooks=caches[0].codebooks,
+                             k_pages=caches[0].k_pages, v_pool=caches[0].v_pool, radius_fmt=caches[0].radius_fmt)
+        alt_out = pkg.decode_paged(q_dev[0], alt, rope, n_ctas=n_alt).float()
+        self_check = max(self_check, float((alt_out - ref_out).abs().max().item()))
+    torch.cuda.synchronize()
+
     def sweep():
         for layer in range(NL):
             pkg.decode_paged(q_dev[layer], caches[layer], rope, out=out_dev[layer])
@@ -442,7 +453,7 @@ def main() -> None:
             "achieved_hbm_gbs_all_gpus": achieved * world,
             "token_heads_per_layer_step": tok_heads,
             "encode": {"ms_per_layer": enc_avg, "token_heads_per_s": tok_heads / (enc_avg * 1e-3)},
-            "kernel_status": status,
+            "kernel_status": status, "split_invariance_max_abs": self_check,
         }
         if not args.no_cpu_baseline and world == 1:
             threads = os.cpu_count() or 1

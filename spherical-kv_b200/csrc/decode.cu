@@ -28,8 +28,20 @@
 
 namespace sphkv {
 
-constexpr int kWarps = 12;
-constexpr int kVStages = 2;
+#ifndef SPHKV_WARPS
+#define SPHKV_WARPS 12
+#endif
+#ifndef SPHKV_CB_DUP
+#define SPHKV_CB_DUP 0  // 1: store every codebook sub-row twice (bank-conflict-free gathers; measured slower)
+#endif
+constexpr int kWarps = SPHKV_WARPS;
+constexpr int kCbPitch = SPHKV_CB_DUP ? 128 : 64;  // bytes per 16-dim codebook sub-row slot
+#ifndef SPHKV_VSTAGES
+#define SPHKV_VSTAGES 3
+#endif
+constexpr int kVStages = SPHKV_VSTAGES;  // V tiles in flight per warp: tile k + kVStages - 1 is
+                                         // copied while tile k is consumed, so >= 2
+static_assert(kVStages >= 2, "the V ring needs a stage to fill while another is read");
 constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
 constexpr int kMaxUnitsInKernelPlan = 2048;
 
@@ -197,7 +209,7 @@ __device__ __forceinline__ void unpack_t(const KWords& w, const TileMeta& m, int
     const uint32_t row = (((uint32_t)(gam0 + i) << bits) + code) * SPG;
 #pragma unroll
     for (int s2 = 0; s2 < SPG; ++s2)
-      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * 128u, __float_as_uint(rad));
+      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * (uint32_t)kCbPitch, __float_as_uint(rad));
   }
   uint2* dst = unp + ut * KS + gam0 * SPG;  // 16-byte aligned: KS and NG*SPG are even
 #pragma unroll
@@ -287,7 +299,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
   uint8_t* v_ring = smem + warp * V_WARP;
   uint8_t* cb_smem = smem + smem_v_bytes(DH);
-  const uint8_t* cb_lane = cb_smem + j * 16 + (r & 1) * 64;  // this lane's chunk of its copy
+  const uint8_t* cb_lane = cb_smem + j * 16 + (SPHKV_CB_DUP ? (r & 1) * 64 : 0);  // this lane's chunk of its copy
   uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [2][KS][32]
   uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) + warp * smem_priv_bytes(DH);
   uint2* unp = reinterpret_cast<uint2*>(warp_priv);                       // [16][KS]
@@ -511,8 +523,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           // shared-memory wavefront never meet in a bank
           const float4 w0 = make_float4(v0.x, v0.y, v2.x, v2.y), w1 = make_float4(v0.z, v0.w, v2.z, v2.w);
           const float4 w2 = make_float4(v1.x, v1.y, v3.x, v3.y), w3 = make_float4(v1.z, v1.w, v3.z, v3.w);
-          dst[row * 8 + 0] = w0; dst[row * 8 + 1] = w1; dst[row * 8 + 2] = w2; dst[row * 8 + 3] = w3;
-          dst[row * 8 + 4] = w0; dst[row * 8 + 5] = w1; dst[row * 8 + 6] = w2; dst[row * 8 + 7] = w3;
+          constexpr int SL = kCbPitch / 16;
+          dst[row * SL + 0] = w0; dst[row * SL + 1] = w1; dst[row * SL + 2] = w2; dst[row * SL + 3] = w3;
+          if (SPHKV_CB_DUP) {
+            dst[row * SL + 4] = w0; dst[row * SL + 5] = w1; dst[row * SL + 6] = w2; dst[row * SL + 7] = w3;
+          }
         }
       }
       cb_head_loaded = hkv;
@@ -562,8 +577,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
     stage_q();
     meta_stage2(0);
     __syncthreads();
-    issue_v(0);
-    issue_v(1);
+#pragma unroll
+    for (int i = 0; i < kVStages - 1; ++i) issue_v(i);
     KWords cur, nx;
     int pos_c[2], pos_1[2], pos_2[2];  // positions of tiles k, k+1, k+2
     load_kwords(0, cur);
@@ -578,7 +593,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         else if (ph == 5) meta_stage1();
         else if (ph == 10) { meta_stage2(kb); __syncwarp(); }
       }
-      issue_v(k + 2);
+      issue_v(k + kVStages - 1);  // into the stage tile k - 1 has just released
       load_kwords(k + 1, nx);
       load_pos(k + 2, pos_2);
       const TileMeta m = get_meta(k);
@@ -732,7 +747,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             }
           }
         }
-        cp_async_wait<2>();
+        cp_async_wait<kVStages - 1>();  // tile k's copy has landed (later ones may be in flight)
         __syncwarp();
         {
           const uint32_t* ph32 = reinterpret_cast<const uint32_t*>(pbuf);
@@ -763,7 +778,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         __syncwarp();
       } else {
         issue_cs(pos_1);
-        cp_async_wait<2>();
+        cp_async_wait<kVStages - 1>();
         __syncwarp();
       }
       cur = nx;
@@ -960,7 +975,7 @@ static int smem_cb_layout(const sphkv_tiers& t, int dh, int* offs) {
   int off = 0;
   for (int s = 0; s < t.n_slots; ++s) {
     offs[s] = off;
-    off += dh * (1 << t.bits[s]) * 4 * 2;  // every sub-row twice
+    off += dh * (1 << t.bits[s]) * 4 * (kCbPitch / 64);
   }
   return off;
 }

@@ -129,6 +129,18 @@ def test_decode_split_invariance(n_ctas):
     check_against_oracle(cache, cbs, Q, ctx, dh, n_ctas=n_ctas)
 
 
+@pytest.mark.parametrize("n_ctas", [1, 2, 5])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_decode_long_runs_per_warp(n_ctas, page_size):
+    """few CTAs over a long context: every warp walks dozens of tiles, so the V ring, the
+    metadata ring refills and the register pipelines all wrap around many times"""
+    ctx, dh = 6000, 128
+    cache, cbs, K, V, Q, _ = build(1, 8, 2, dh, ctx, page_size, pkg.REFERENCE_TIERS, {1: 0.3, 2: 0.5, 3: 0.1},
+                                   v_dtype=torch.bfloat16, seed=41)
+    cache.scratch = None
+    check_against_oracle(cache, cbs, Q, ctx, dh, n_ctas=n_ctas)
+
+
 def test_decode_ragged_units_holes_and_empty():
     """units of very different length, one empty unit, holes (-1) inside a block list,
     single-token pages, spare block-table columns"""
