@@ -298,12 +298,13 @@ def main() -> None:
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=CFG["layers"])
     ap.add_argument("--ctx", type=int, default=CFG["ctx"])
+    ap.add_argument("--batch", type=int, default=CFG["B"], help="batch rows per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", default="decode", choices=["decode", "splitkv", "encode"],
                     help="decode: the headline line (default); splitkv: one 131072-token sequence "
                          "split over the ranks; encode: prefill compression throughput")
     args = ap.parse_args()
-    CFG["layers"], CFG["ctx"] = args.layers, args.ctx
+    CFG["layers"], CFG["ctx"], CFG["B"] = args.layers, args.ctx, args.batch
     if args.impl == "reference":
         run_reference(args)
         return
