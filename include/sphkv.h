@@ -229,6 +229,14 @@ int sphkv_ragged_logits(const uint8_t* pages, const int32_t* ptable, const int32
                         int32_t page_size, int32_t n_pages, int32_t Hq, int32_t table_rows,
                         int32_t radius_fmt, int32_t reserved, void* stream);
 
+/* Replaces _omega_ema_eager / _update_omega_gpu (spherical_kv_pipeline.py:952-987,
+ * 1669-1701): page-level importance EMA from the per-block (m, l) the decode kernels emit.
+ * ml: element (query head hq, block blk) at ml[(hq*max_blocks + blk)*stride + {0,1}] (stride =
+ * dh+2 for partial_scratch of sphkv_pool_decode, 2 for page_ml of sphkv_decode_paged); omega
+ * f32 [n_units][max_blocks] is updated in place: omega*beta + mean_group(mass)*(1-beta). */
+int sphkv_omega_ema(const float* ml, float* omega, int32_t n_units, int32_t kv_groups,
+                    int32_t max_blocks, int32_t stride, float beta, void* stream);
+
 /* ---- Library ---------------------------------------------------------------------*/
 int sphkv_abi_version(void);
 const char* sphkv_last_error(void);

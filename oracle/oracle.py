@@ -364,3 +364,14 @@ def qlut_logits(q_lut, theta_codes, radius_codes, r_scales, block_table, bits_ta
             ok = (s != 0) & (t_idx < int(ctx_lens[hkv]))
             out[hq, t_idx[ok]] = s[ok] * sm_scale
     return out
+
+
+def omega_ema(m_q, l_q, omega_prev, num_kv: int, kv_groups: int, max_blocks: int, ema_beta: float):
+    """_omega_ema_eager (spherical_kv_pipeline.py:952-987), op for op."""
+    valid = l_q > 0
+    m_safe = torch.where(valid, m_q, m_q.new_full((), -1e30))
+    m_max = m_safe.amax(dim=1, keepdim=True)
+    w = (m_safe - m_max).clamp_min(-60.0).exp() * l_q
+    Z = w.sum(dim=1, keepdim=True).clamp_min(1e-12)
+    page_mass_kv = (w / Z).view(num_kv, kv_groups, max_blocks).mean(dim=1)
+    return omega_prev * ema_beta + page_mass_kv * (1.0 - ema_beta)

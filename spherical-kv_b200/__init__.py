@@ -13,8 +13,8 @@ from .pages import (PagedCache, PageLists, REFERENCE_TIERS, TierSet, TierSpec,  
                     build_page_lists, shard_block_lists)
 from . import split_kv  # noqa: F401
 from .ops import (decode_paged, decode_scratch, encode_pages, hf_inv_freq,  # noqa: F401
-                  merge_partials, rope_table)
+                  merge_partials, omega_ema, rope_table)
 
 __all__ = ["SphKVError", "RADIUS_F16", "RADIUS_I8", "PagedCache", "PageLists", "REFERENCE_TIERS",
            "TierSet", "TierSpec", "build_page_lists", "shard_block_lists", "decode_paged", "decode_scratch",
-           "encode_pages", "hf_inv_freq", "merge_partials", "rope_table"]
+           "encode_pages", "hf_inv_freq", "merge_partials", "omega_ema", "rope_table"]

@@ -77,6 +77,8 @@ SIGNATURES = {
     "sphkv_pool_encode_append": (C.c_int, [C.c_void_p] * 8 + [C.c_int32] * 9 + [C.c_void_p]),
     "sphkv_qlut_logits": (C.c_int, [C.c_void_p] * 8 + [C.c_int32] * 8 + [C.c_float, C.c_int32,
                                                                         C.c_void_p]),
+    "sphkv_omega_ema": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                  C.c_float, C.c_void_p]),
     "sphkv_ragged_logits": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 12 + [C.c_void_p]),
 }
 

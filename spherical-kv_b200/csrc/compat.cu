@@ -397,3 +397,97 @@ extern "C" int sphkv_ragged_logits(const uint8_t* pages, const int32_t* ptable,
       dh, G, g, b_theta, page_size, n_pages, Hq, table_rows, radius_fmt);
   return check_launch("ragged_logits_kernel");
 }
+
+// ---- page-level importance EMA from per-block (m, l) --------------------------------------------
+// _omega_ema_eager (spherical_kv_pipeline.py:952-987) in one launch: per query head the block
+// weights exp(max(m - m_max, -60)) * l are normalised over the blocks, averaged over the query
+// heads of a KV head and blended into omega with factor beta.  ml points at the (m, l) pairs of
+// (query head, block): element (hq, blk) lives at ml[(hq * max_blocks + blk) * stride + {0, 1}]
+// (stride = dh + 2 for the partial_scratch of sphkv_pool_decode, 2 for page_ml of
+// sphkv_decode_paged).  omega [n_units][max_blocks] is updated in place; unit u owns query heads
+// u * kv_groups .. (u + 1) * kv_groups - 1.
+namespace sphkv {
+__global__ void omega_ema_kernel(const float* __restrict__ ml, float* __restrict__ omega,
+                                 int kv_groups, int max_blocks, int stride, float beta) {
+  const int u = blockIdx.x;
+  __shared__ float s_red[32];
+  __shared__ float s_val;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  auto block_reduce = [&](float v, bool is_max) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float t = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, t) : v + t;
+    }
+    if (lane == 0) s_red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      float x = lane < nw ? s_red[lane] : (is_max ? -INFINITY : 0.f);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float t = __shfl_xor_sync(0xffffffffu, x, o);
+        x = is_max ? fmaxf(x, t) : x + t;
+      }
+      if (lane == 0) s_val = x;
+    }
+    __syncthreads();
+    const float r = s_val;
+    __syncthreads();
+    return r;
+  };
+  // mass accumulated over the group's query heads, blocks strided over the threads
+  extern __shared__ float s_mass[];  // [max_blocks]
+  for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) s_mass[i] = 0.f;
+  __syncthreads();
+  for (int h = 0; h < kv_groups; ++h) {
+    const float* base = ml + ((int64_t)(u * kv_groups + h) * max_blocks) * stride;
+    float mx = -1e30f;
+    for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) {
+      const float m = base[(int64_t)i * stride], l = base[(int64_t)i * stride + 1];
+      mx = fmaxf(mx, l > 0.f ? m : -1e30f);
+    }
+    mx = block_reduce(mx, true);
+    float z = 0.f;
+    for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) {
+      const float m = base[(int64_t)i * stride], l = base[(int64_t)i * stride + 1];
+      const float ms = l > 0.f ? m : -1e30f;
+      z += __expf(fmaxf(ms - mx, -60.f)) * l;
+    }
+    z = fmaxf(block_reduce(z, false), 1e-12f);
+    for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) {
+      const float m = base[(int64_t)i * stride], l = base[(int64_t)i * stride + 1];
+      const float ms = l > 0.f ? m : -1e30f;
+      s_mass[i] += __expf(fmaxf(ms - mx, -60.f)) * l / z;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) {
+    float* o = omega + (int64_t)u * max_blocks + i;
+    *o = *o * beta + (s_mass[i] / (float)kv_groups) * (1.0f - beta);
+  }
+}
+}  // namespace sphkv
+
+extern "C" int sphkv_omega_ema(const float* ml, float* omega, int32_t n_units, int32_t kv_groups,
+                               int32_t max_blocks, int32_t stride, float beta, void* stream) {
+  SPHKV_REQUIRE(ml && omega, SPHKV_E_ARG, "omega_ema: NULL pointer");
+  SPHKV_REQUIRE(n_units > 0 && kv_groups > 0 && max_blocks > 0 && stride >= 2, SPHKV_E_ARG,
+                "omega_ema: n_units=%d kv_groups=%d max_blocks=%d stride=%d", n_units, kv_groups,
+                max_blocks, stride);
+  SPHKV_REQUIRE((size_t)max_blocks * 4 <= 160 * 1024, SPHKV_E_LIMIT,
+                "omega_ema: max_blocks=%d exceeds 40960", max_blocks);
+  const size_t smem = (size_t)max_blocks * 4;
+  static size_t configured = 48 * 1024;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(sphkv::omega_ema_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      sphkv::set_error("omega_ema: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = smem;
+  }
+  sphkv::omega_ema_kernel<<<n_units, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ml, omega, kv_groups, max_blocks, stride, beta);
+  return sphkv::check_launch("omega_ema_kernel");
+}

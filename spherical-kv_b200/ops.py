@@ -163,3 +163,16 @@ def merge_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32,
     _lib.check(lib.sphkv_merge_partials(parts.data_ptr(), R, n_rows, dh, out.data_ptr(),
                                         _DT[out.dtype], _stream()), "sphkv_merge_partials")
     return out
+
+
+def omega_ema(ml: torch.Tensor, omega: torch.Tensor, kv_groups: int, beta: float = 0.9) -> torch.Tensor:
+    """In-place page-importance EMA (spherical_kv_pipeline.py:952-987).  ml: [n_q, max_blocks, S]
+    with (m, l) in channels 0 and 1 (the partial_scratch of sphkv_decode, S = dh+2, or the page_ml
+    of decode_paged flattened over batch, S = 2); omega: f32 [n_q / kv_groups, max_blocks]."""
+    lib = _lib.load()
+    _need_cuda(ml, omega)
+    n_q, max_blocks, stride = ml.shape
+    assert omega.shape == (n_q // kv_groups, max_blocks) and omega.dtype == torch.float32
+    _lib.check(lib.sphkv_omega_ema(ml.data_ptr(), omega.data_ptr(), n_q // kv_groups, kv_groups, max_blocks,
+                                   stride, float(beta), _stream()), "sphkv_omega_ema")
+    return omega

@@ -210,3 +210,22 @@ def test_fused_decode_ragged_logits(fd, tier):
         assert (g_blk[h * grp:(h + 1) * grp, :c] - want).abs().max().item() <= 2e-4
         other = torch.ones(Hq, dtype=torch.bool); other[h * grp:(h + 1) * grp] = False
         assert (g_blk[other] == 0).all() and (g_blk[:, c:] == 0).all()
+
+
+@pytest.mark.parametrize("stride", [2, 130])
+def test_omega_ema_matches_reference_formula(stride):
+    """page-importance EMA from per-block (m, l): spherical_kv_pipeline.py:952-987"""
+    Hkv, grp, max_blocks = 3, 4, 77
+    g = torch.Generator().manual_seed(8)
+    ml = torch.zeros(Hkv * grp, max_blocks, stride)
+    ml[..., 0] = torch.randn(Hkv * grp, max_blocks, generator=g) * 3
+    ml[..., 1] = torch.rand(Hkv * grp, max_blocks, generator=g) * 16
+    dead = torch.rand(Hkv * grp, max_blocks, generator=g) < 0.2       # empty blocks: m = -inf, l = 0
+    ml[..., 0][dead] = -float("inf"); ml[..., 1][dead] = 0
+    ml[5, :, 1] = 0; ml[5, :, 0] = -float("inf")                      # a head with no live block
+    omega = torch.rand(Hkv, max_blocks, generator=g)
+    want = orc.omega_ema(ml[..., 0], ml[..., 1], omega, Hkv, grp, max_blocks, 0.9)
+    od = omega.clone().to(DEV)
+    pkg.omega_ema(ml.to(DEV), od, grp, 0.9)
+    torch.cuda.synchronize()
+    assert (od.cpu() - want).abs().max().item() <= 1e-6
