@@ -493,6 +493,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         const float4* rp = reinterpret_cast<const float4*>(p.rope_table + (int64_t)pos * DH) + j * 2;
 #pragma unroll
         for (int s = 0; s < HS; ++s) {
+          // through L1 on purpose: a lane's cos and sin vectors share a 32-byte sector
           cs[tk][s][0] = __ldg(rp + s * 8);
           cs[tk][s][1] = __ldg(rp + s * 8 + 1);
         }
