@@ -206,6 +206,38 @@ int sphkv_pool_encode_append(const float* k_post, const float* v_new, const floa
                              int32_t C, int32_t G_max, int32_t dh, int32_t page_size,
                              int32_t is_new_page, int32_t num_kv, void* stream);
 
+/* ---- Device-resident LayerPool management -------------------------------------------
+ * Bookkeeping that the reference does on the host each decode step, done by the GPU so a
+ * step needs no host reads, no uploads and can be recorded into a CUDA graph. */
+
+/* Bulk construction of pool pages from encode output; replaces the per-page Python loop of
+ * LayerPool.__init__ (sphkv_lut.py:37-68, arithmetic of :50-60).  r f32 and theta u8 are
+ * [rows][code_stride], v_src [rows][v_stride] of v_dtype.  page_desc i32 [n_pages][4] =
+ * {src_row, n_rows, G_t, dst_pid} (16-byte aligned): rows src_row .. src_row+n_rows fill the
+ * first n_rows slots and G_t groups of page dst_pid; the rest of that page is zeroed.
+ * Per page and group: scale = max(max_t r, 1e-8), code = clamp(rint(r / scale * 255)). */
+int sphkv_pool_build_pages(const float* r, const uint8_t* theta, const void* v_src, int32_t v_dtype,
+                           int64_t code_stride, int64_t v_stride, const int32_t* page_desc,
+                           int32_t n_pages, uint8_t* theta_codes, uint8_t* radius_codes,
+                           float* r_scales, void* v_pool, int32_t page_size, int32_t G_max,
+                           int32_t dh, void* stream);
+
+/* One decode-step append with the bookkeeping of LayerPool.append_and_compute
+ * (sphkv_lut.py:150-186) on the device: state i32 [4] = {uniform context length, pages in
+ * use, internal ticket (0 between calls), error flag}.  slot = ctx % page_size; when slot is 0
+ * head h claims page used+h, writes block_table[h][ctx / page_size] and
+ * bits_table[..] = dec_tier_idx and pids[h]; then the token is encoded and appended exactly as
+ * sphkv_pool_encode_append does, ctx_lens[h] += 1, and the state advances.  A step that
+ * would exceed n_pool_pages or max_blocks changes nothing except state[3] = 1, after which
+ * every later step is a no-op; the caller reads state[3] whenever it next synchronises. */
+int sphkv_pool_append_step(const float* k_post, const float* v_new, const float* decode_cb,
+                           uint8_t* theta_codes, uint8_t* radius_codes, float* r_scales,
+                           void* v_pool, int32_t* block_table, int32_t* bits_table,
+                           int32_t* ctx_lens, int64_t* pids, int32_t* state, int32_t dec_tier_idx,
+                           int32_t G, int32_t g, int32_t C, int32_t G_max, int32_t dh,
+                           int32_t page_size, int32_t num_kv, int32_t max_blocks,
+                           int32_t n_pool_pages, void* stream);
+
 /* Implements the launcher new_fused_decode.cpp:3-22 declares and the reference never
  * defines: logits from a q.centroid table.  q_lut f32 [Hq][num_tiers][G_max][cb_size_max];
  * logits_out f32 [Hq][max_blocks*page_size]; holes, slots past ctx_lens and exact-zero

@@ -375,3 +375,68 @@ def omega_ema(m_q, l_q, omega_prev, num_kv: int, kv_groups: int, max_blocks: int
     Z = w.sum(dim=1, keepdim=True).clamp_min(1e-12)
     page_mass_kv = (w / Z).view(num_kv, kv_groups, max_blocks).mean(dim=1)
     return omega_prev * ema_beta + page_mass_kv * (1.0 - ema_beta)
+
+
+def pool_build(segments, tiers, tier_idx_map, num_kv: int, page_size: int, G_max: int, dh: int,
+               decode_capacity: int):
+    """LayerPool.__init__ page construction (sphkv_lut.py:33-103) on the CPU.
+
+    segments[h] = list of (b_theta, n_tokens, V [n, dh], r [n, G_t] f32, theta [n, G_t]) in page
+    order; tiers = list of dicts {tier_id, G, g, b_theta} of the compressed tiers.  Returns the
+    four pool arrays, the block and bits tables, ctx_lens and (n_used, max_blocks)."""
+    pages, head_blocks = [], [[] for _ in range(num_kv)]
+    for h in range(num_kv):
+        for b_theta, n_tokens, V, r_full, theta_full in segments[h]:
+            tier = next(t for t in tiers if t["b_theta"] == b_theta)
+            t_idx, G_t = tier_idx_map[tier["tier_id"]], tier["G"]
+            for pg in range((n_tokens + page_size - 1) // page_size):
+                s, e = pg * page_size, min((pg + 1) * page_size, n_tokens)
+                th = torch.zeros(page_size, G_max, dtype=torch.uint8)
+                rq = torch.zeros(page_size, G_max, dtype=torch.uint8)
+                sc = torch.zeros(G_max, dtype=torch.float32)
+                chunk = r_full[s:e].float()
+                scale = chunk.amax(dim=0).clamp(min=1e-8)
+                th[:e - s, :G_t] = theta_full[s:e].to(torch.uint8)
+                rq[:e - s, :G_t] = (chunk / scale * 255.0).round().clamp(0, 255).to(torch.uint8)
+                sc[:G_t] = scale
+                v = torch.zeros(page_size, dh, dtype=torch.float16)
+                v[:e - s] = V[s:e].half()
+                head_blocks[h].append((len(pages), t_idx))
+                pages.append((th, rq, sc, v))
+    n_used = len(pages)
+    n_total = n_used + decode_capacity
+    max_blocks = max((len(b) for b in head_blocks), default=0) + decode_capacity // max(num_kv, 1) + 2
+    theta_codes = torch.zeros(n_total, page_size, G_max, dtype=torch.uint8)
+    radius_codes = torch.zeros(n_total, page_size, G_max, dtype=torch.uint8)
+    r_scales = torch.zeros(n_total, G_max, dtype=torch.float32)
+    v_pool = torch.zeros(n_total, page_size, dh, dtype=torch.float16)
+    for pid, (th, rq, sc, v) in enumerate(pages):
+        theta_codes[pid], radius_codes[pid], r_scales[pid], v_pool[pid] = th, rq, sc, v
+    block_table = torch.full((num_kv, max_blocks), -1, dtype=torch.int32)
+    bits_table = torch.zeros((num_kv, max_blocks), dtype=torch.int32)
+    for h, blocks in enumerate(head_blocks):
+        for lb, (pid, ti) in enumerate(blocks):
+            block_table[h, lb], bits_table[h, lb] = pid, ti
+    ctx_lens = torch.tensor([len(b) * page_size for b in head_blocks], dtype=torch.int32)
+    return theta_codes, radius_codes, r_scales, v_pool, block_table, bits_table, ctx_lens, n_used, max_blocks
+
+
+def pool_append_bookkeeping(state: dict, block_table, bits_table, pids, num_kv: int, page_size: int,
+                            dec_tier_idx: int):
+    """Host bookkeeping of LayerPool.append_and_compute (sphkv_lut.py:153-170), in place.
+
+    state = {"ctx": uniform context length, "used": pages in use}.  Returns (slot, is_new_page)
+    to hand to pool_encode_append; the caller then adds 1 to every ctx_lens entry (:186)."""
+    cur = state["ctx"]
+    slot = cur % page_size
+    is_new = slot == 0
+    if is_new:
+        pg = cur // page_size
+        start = state["used"]
+        state["used"] = start + num_kv
+        for h in range(num_kv):
+            block_table[h, pg] = start + h
+            bits_table[h, pg] = dec_tier_idx
+            pids[h] = start + h
+    state["ctx"] = cur + 1
+    return slot, is_new

@@ -80,6 +80,9 @@ SIGNATURES = {
     "sphkv_omega_ema": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                   C.c_float, C.c_void_p]),
     "sphkv_ragged_logits": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 12 + [C.c_void_p]),
+    "sphkv_pool_build_pages": (C.c_int, [C.c_void_p] * 3 + [C.c_int32, C.c_int64, C.c_int64, C.c_void_p,
+                                         C.c_int32] + [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p]),
+    "sphkv_pool_append_step": (C.c_int, [C.c_void_p] * 12 + [C.c_int32] * 10 + [C.c_void_p]),
 }
 
 _lib = None

@@ -114,4 +114,63 @@ __host__ __device__ __forceinline__ int64_t cta_range_start(int c, int n, int64_
   return (int64_t)c * T / n;
 }
 
+// One token of one KV head appended to a LayerPool page (decode_kernel.cu:10-84): nearest
+// centroid per group on the normalised key, running-max radius scale with in-place
+// re-quantisation of the slots already in the page, fp16 value row.  Called by every thread
+// of a CTA of 32 * G threads (warp = group, lanes split the centroids); blockIdx.x = KV head.
+__device__ __forceinline__ void pool_append_token(
+    const float* __restrict__ k_post, const float* __restrict__ v_new,
+    const float* __restrict__ decode_cb, uint8_t* __restrict__ theta_codes,
+    uint8_t* __restrict__ radius_codes, float* __restrict__ r_scales, __half* __restrict__ v_pool,
+    int64_t pid, int slot, int G, int g, int C, int G_max, int dh, int page_size, int is_new_page) {
+  const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t v_base = (pid * page_size + slot) * dh;
+  const int64_t code_base = (pid * page_size + slot) * G_max;
+  for (int d = tid; d < dh; d += blockDim.x) v_pool[v_base + d] = __float2half(v_new[(int64_t)h * dh + d]);
+  if (warp >= G) return;
+  const int grp = warp;
+  const float* k_g = k_post + (int64_t)h * dh + grp * g;
+  float norm_sq = 0.f;
+  for (int d = 0; d < g; ++d) norm_sq += k_g[d] * k_g[d];
+  const float norm = sqrtf(norm_sq + 1e-16f);
+  const float inv_norm = 1.0f / (norm + 1e-8f);
+  const float* cb = decode_cb + ((int64_t)h * G * C + (int64_t)grp * C) * g;
+  float best_sim = -1e30f;
+  int best_code = 0;
+  for (int c = lane; c < C; c += 32) {  // ascending per lane: strict > keeps the lowest index
+    float sim = 0.f;
+    for (int d = 0; d < g; ++d) sim += k_g[d] * inv_norm * cb[(int64_t)c * g + d];
+    if (sim > best_sim) { best_sim = sim; best_code = c; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float os = __shfl_xor_sync(0xffffffffu, best_sim, o);
+    const int oc = __shfl_xor_sync(0xffffffffu, best_code, o);
+    if (os > best_sim || (os == best_sim && oc < best_code)) { best_sim = os; best_code = oc; }
+  }
+  float r_scale;
+  const float prev_scale = is_new_page ? 0.f : r_scales[pid * G_max + grp];
+  if (is_new_page || norm > prev_scale) {
+    if (!is_new_page) {
+      const float ratio = prev_scale / (norm + 1e-8f);
+      for (int t = lane; t < slot; t += 32) {
+        const int64_t idx = (pid * page_size + t) * G_max + grp;
+        float rescaled = (float)radius_codes[idx] * ratio;
+        rescaled = fminf(fmaxf(roundf(rescaled), 0.f), 255.f);
+        radius_codes[idx] = (uint8_t)rescaled;
+      }
+    }
+    r_scale = norm;
+  } else {
+    r_scale = prev_scale;
+  }
+  if (lane == 0) {
+    theta_codes[code_base + grp] = (uint8_t)best_code;
+    if (is_new_page || norm > prev_scale) r_scales[pid * G_max + grp] = norm;
+    float r_q = roundf(norm / (r_scale + 1e-8f) * 255.0f);
+    r_q = fminf(fmaxf(r_q, 0.f), 255.f);
+    radius_codes[code_base + grp] = (uint8_t)r_q;
+  }
+}
+
 }  // namespace sphkv

@@ -122,3 +122,56 @@ def test_c_encode_vs_reference_style_encode():
         r2, th2 = orc.encode_reference_style(K, cb)
         assert _ulps(r, r2.numpy()).max() <= 4
         assert (th != th2.numpy()).mean() < 1e-3
+
+
+# ---- LayerPool construction and append bookkeeping (sphkv_lut.py) ------------------------------
+def _pool_golden():
+    z = np.load(os.path.join(GOLDEN, "layer_pool.npz"))
+    num_kv, grp, dh, page, cap, steps, G_max, cb_max = (int(x) for x in z["shape"])
+    tiers = [dict(tier_id=t.tier_id, G=dh // t.g, g=t.g, b_theta=t.b_theta) for t in pkg.REFERENCE_TIERS]
+    idx_map = {int(k): int(v) for k, v in z["tier_idx"]}
+    segments = []
+    for h in range(num_kv):
+        segs = []
+        for si in range(int(z[f"h{h}_nseg"])):
+            tier = next(t for t in tiers if t["tier_id"] == int(z[f"h{h}_s{si}_tier"]))
+            r = torch.from_numpy(z[f"h{h}_s{si}_r"])
+            segs.append((tier["b_theta"], r.shape[0], torch.from_numpy(z[f"h{h}_s{si}_v"]), r,
+                         torch.from_numpy(z[f"h{h}_s{si}_theta"])))
+        segments.append(segs)
+    return z, tiers, idx_map, segments, (num_kv, grp, dh, page, cap, steps, G_max, cb_max)
+
+
+def test_pool_build_matches_reference_layerpool():
+    """oracle.pool_build == LayerPool.__init__ of the reference, byte for byte (incl. partial
+    pages, a zero radius and an all-zero group)"""
+    z, tiers, idx_map, segments, (num_kv, grp, dh, page, cap, steps, G_max, cb_max) = _pool_golden()
+    th, rq, sc, v, bt, bi, ctx, n_used, max_blocks = orc.pool_build(segments, tiers, idx_map, num_kv, page,
+                                                                   G_max, dh, cap)
+    assert n_used == int(z["n_used0"]) and max_blocks == int(z["max_blocks"])
+    np.testing.assert_array_equal(th.numpy(), z["theta_codes"])
+    np.testing.assert_array_equal(rq.numpy(), z["radius_codes"])
+    np.testing.assert_array_equal(sc.numpy(), z["r_scales"])
+    np.testing.assert_array_equal(v.numpy(), z["v_pool"])
+    np.testing.assert_array_equal(bt.numpy(), z["block_table0"])
+    np.testing.assert_array_equal(bi.numpy(), z["bits_table0"])
+    np.testing.assert_array_equal(ctx.numpy(), z["ctx_lens0"])
+
+
+def test_pool_append_bookkeeping_matches_reference():
+    """slot / is_new_page / pids of every step and the tables after 20 steps == the reference's
+    host bookkeeping (two page roll-overs)"""
+    z, tiers, idx_map, segments, (num_kv, grp, dh, page, cap, steps, G_max, cb_max) = _pool_golden()
+    bt, bi = torch.from_numpy(z["block_table0"].copy()), torch.from_numpy(z["bits_table0"].copy())
+    ctx = z["ctx_lens0"].copy()
+    state = dict(ctx=int(ctx[0]), used=int(z["n_used0"]))
+    pids = torch.zeros(num_kv, dtype=torch.int64)
+    for s in range(steps):
+        slot, is_new = orc.pool_append_bookkeeping(state, bt, bi, pids, num_kv, page, idx_map[1])
+        ctx += 1
+        assert slot == int(z["step_slot"][s]) and int(is_new) == int(z["step_is_new"][s])
+        np.testing.assert_array_equal(pids.numpy(), z["step_pids"][s])
+    np.testing.assert_array_equal(bt.numpy(), z["block_table1"])
+    np.testing.assert_array_equal(bi.numpy(), z["bits_table1"])
+    np.testing.assert_array_equal(ctx, z["ctx_lens1"])
+    assert state["used"] == int(z["n_used1"]) and state["ctx"] == int(z["ctx1"])
