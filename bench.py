@@ -160,7 +160,8 @@ def workload_config(args) -> dict:
             "B_per_gpu": CFG["B"], "Hq": CFG["Hq"], "Hkv": CFG["Hkv"], "dh": CFG["dh"], "ctx": CFG["ctx"],
             "layers": CFG["layers"], "page_size": CFG["page_size"], "budget_bits": args.budget,
             "l2_policy": "32 distinct layer caches (>= 8 GB) cycled per step: inputs larger than L2",
-            "sharding": "batch rows per GPU, no collective"}
+            "sharding": "batch rows per GPU, no collective",
+            "page_importance_ema": bool(getattr(args, "ema", False))}
 
 
 def run_side_workload(args) -> None:
@@ -300,6 +301,9 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=CFG["ctx"])
     ap.add_argument("--batch", type=int, default=CFG["B"], help="batch rows per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ema", action="store_true",
+                    help="also update the page-importance EMA in the decode epilogue (per-tile statistics + "
+                         "omega blend inside the merge kernel); off for the headline line")
     ap.add_argument("--workload", default="decode", choices=["decode", "splitkv", "encode"],
                     help="decode: the headline line (default); splitkv: one 131072-token sequence "
                          "split over the ranks; encode: prefill compression throughput")
@@ -368,9 +372,17 @@ def main() -> None:
         self_check = max(self_check, float((alt_out - ref_out).abs().max().item()))
     torch.cuda.synchronize()
 
+    if args.ema:
+        tile_ml = [torch.empty(B, Hq, c.lists.max_blocks, N // 16, 2, device=dev) for c in caches]
+        omegas = [torch.ones(B * Hkv, c.lists.max_blocks, device=dev) for c in caches]
+
     def sweep():
         for layer in range(NL):
-            pkg.decode_paged(q_dev[layer], caches[layer], rope, out=out_dev[layer])
+            if args.ema:
+                pkg.decode_paged(q_dev[layer], caches[layer], rope, out=out_dev[layer], page_ml=tile_ml[layer],
+                                 omega=omegas[layer], ema_beta=0.9)
+            else:
+                pkg.decode_paged(q_dev[layer], caches[layer], rope, out=out_dev[layer])
 
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):

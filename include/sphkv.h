@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SPHKV_ABI_VERSION 1
+#define SPHKV_ABI_VERSION 2
 
 /* error codes */
 #define SPHKV_OK 0
@@ -130,20 +130,27 @@ typedef struct sphkv_decode_params {
   float* out_partial;         /* optional [B][Hq][dh+2]: (max, sum, acc) un-normalised,
                                  natural-log max, the triple of decode_kernel.cu:212-217
                                  taken over the whole local context                   */
-  float* page_ml;             /* optional [B][Hq][max_blocks][2] per-block (max, sum),
-                                 natural-log domain, the side output read at
-                                 spherical_kv_pipeline.py:1690-1693; only written for
-                                 page_size == 16                                      */
+  float* page_ml;             /* optional [B][Hq][max_blocks][page_size/16][2]: (max, sum)
+                                 of every 16-token tile of every block in use, natural-
+                                 log domain ((-inf, 0) for a tile without tokens); with
+                                 page_size 16 this is the per-block side output read at
+                                 spherical_kv_pipeline.py:1690-1693                   */
   float* logits_out;          /* optional [B][Hq][max_blocks*page_size] f32: the scaled
                                  logit of every stored token (slot order of the block
                                  table); slots without a token are left untouched       */
   void* scratch;              /* sphkv_decode_scratch_bytes() bytes, 256-aligned      */
   int64_t scratch_bytes;
   int32_t* status;            /* optional device int, OR-ed with SPHKV_ST_* bits      */
+  float* omega;               /* optional [B*Hkv][max_blocks] page importance, updated in
+                                 place by the merge kernel: omega*ema_beta + (mean over
+                                 the KV head's query heads of the block's softmax mass)
+                                 *(1-ema_beta), the update of _omega_ema_eager
+                                 (spherical_kv_pipeline.py:952-987); needs page_ml      */
   int32_t B, Hq, Hkv, dh, page_size, max_blocks, n_pages, max_pos;
   int32_t q_dtype, v_dtype, out_dtype, radius_fmt;
   int32_t n_ctas;             /* 0 = one per SM of the current device                 */
   float sm_scale;
+  float ema_beta;             /* EMA factor for omega (the reference uses 0.9)        */
   sphkv_tiers tiers;
 } sphkv_decode_params;
 

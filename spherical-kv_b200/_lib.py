@@ -48,13 +48,13 @@ class DecodeParams(C.Structure):
         ("bits_table", C.c_void_p), ("num_blocks", C.c_void_p), ("codebooks", C.c_void_p),
         ("rope_table", C.c_void_p), ("out", C.c_void_p), ("out_partial", C.c_void_p),
         ("page_ml", C.c_void_p), ("logits_out", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("omega", C.c_void_p),
         ("B", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("dh", C.c_int32),
         ("page_size", C.c_int32), ("max_blocks", C.c_int32), ("n_pages", C.c_int32),
         ("max_pos", C.c_int32),
         ("q_dtype", C.c_int32), ("v_dtype", C.c_int32), ("out_dtype", C.c_int32),
         ("radius_fmt", C.c_int32), ("n_ctas", C.c_int32), ("sm_scale", C.c_float),
-        ("tiers", Tiers),
+        ("ema_beta", C.c_float), ("tiers", Tiers),
     ]
 
 
@@ -107,8 +107,8 @@ def load() -> C.CDLL:
         fn.restype = res
         fn.argtypes = args
     ver = lib.sphkv_abi_version()
-    if ver != 1:
-        raise SphKVError(f"libsphkv_b200.so ABI version {ver}, expected 1")
+    if ver != 2:
+        raise SphKVError(f"libsphkv_b200.so ABI version {ver}, expected 2")
     for which, st in enumerate((Tiers, EncodeParams, DecodeParams)):
         if lib.sphkv_struct_size(which) != C.sizeof(st):
             raise SphKVError(f"struct layout mismatch for {st.__name__}: library "

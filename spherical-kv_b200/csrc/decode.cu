@@ -381,6 +381,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
     auto tile_lb = [&](int kk) { return lb0 + ((warp + kWarps * kk) >> tpp_shift); };
     auto tile_sub = [&](int kk) { return (warp + kWarps * kk) & (TPP - 1); };
+    // per-tile statistics of this segment: tile kk of head n lands at ml_seg[n * ml_head + 2 * (warp + 12 kk)]
+    float* ml_seg = nullptr;
+    const int64_t ml_head = (int64_t)p.max_blocks * TPP * 2;
+    if (EXTRA && p.page_ml != nullptr)
+      ml_seg = p.page_ml + ((int64_t)b * p.Hq + (int64_t)hkv * a.grp) * ml_head + ((int64_t)lb0 * TPP + warp) * 2;
 
     // Tile metadata is fetched 16 tiles at a time, lane = tile (lanes 0..15).  The three
     // dependent loads (block table -> pointer table -> page header) are issued in separate
@@ -699,8 +704,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             acc[dt][2] *= alpha[0]; acc[dt][3] *= alpha[1];
           }
         }
-        if (EXTRA && p.page_ml != nullptr && TPP == 1) {
-          // per-block (max, sum) in the natural-log domain for heads 2j, 2j+1
+        if (EXTRA && ml_seg != nullptr) {
+          // per-tile (max, sum) in the natural-log domain for heads 2j, 2j+1
           float ls[2] = {pv[0] + pv[2], pv[1] + pv[3]};
 #pragma unroll
           for (int o = 4; o < 32; o <<= 1) {
@@ -712,8 +717,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
             for (int c = 0; c < 2; ++c) {
               const int n = 2 * j + c;
               if (n < a.grp && (!PACK || j < 2)) {
-                float* dst = p.page_ml + (((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks +
-                                          tile_lb(k)) * 2;
+                float* dst = ml_seg + n * ml_head + 2 * kWarps * k;
                 const float tm = tmax[c];
                 dst[0] = tm * kLn2;
                 dst[1] = (tm == -INFINITY) ? 0.f : ls[c] * fast_exp2(msafe[c] - tm);
@@ -781,6 +785,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         issue_cs(pos_1);
         cp_async_wait<kVStages - 1>();
         __syncwarp();
+        if (EXTRA && ml_seg != nullptr && lane < a.grp) {  // a tile without tokens: (-inf, 0)
+          float* dst = ml_seg + lane * ml_head + 2 * kWarps * k;
+          dst[0] = -INFINITY;
+          dst[1] = 0.f;
+        }
       }
       cur = nx;
       pos_c[0] = pos_1[0]; pos_c[1] = pos_1[1];
@@ -898,6 +907,41 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
     if (lane == 0) { s_M[warp] = M; s_L[warp] = L; }
   }
   __syncthreads();
+  // page-importance EMA (_omega_ema_eager, spherical_kv_pipeline.py:952-987) from the per-tile
+  // (max, sum) the split-K kernel left in page_ml: per query head the block weights
+  // exp(max(m - m_max, -60)) * l are normalised over the blocks, averaged over the heads of
+  // this KV head and blended into omega.  m_max is the head's global maximum found above, and
+  // the normaliser (the sum of the weights over all blocks) is the head's global sum: both
+  // are sums of the same exp(logit - m_max) terms, so no second pass over the blocks is needed
+  // (the -60 clamp changes terms below e^-60 of the largest one).
+  if (p.omega != nullptr) {
+    const int tpp = p.page_size >> 4;
+    const int unit = b * p.Hkv + hkv;
+    const int nb = min(p.num_blocks[unit], p.max_blocks);
+    const int32_t* bt = p.block_table + (int64_t)unit * p.max_blocks;
+    const float one_minus = (1.0f - p.ema_beta) / (float)a.grp;
+    // blocks are spread over gridDim.y CTAs of this unit; each repeats the cheap pass 1
+    for (int blk = blockIdx.y * blockDim.x + threadIdx.x; blk < p.max_blocks; blk += gridDim.y * blockDim.x) {
+      float mass = 0.f;
+      if (blk < nb && bt[blk] >= 0) {
+        for (int n = 0; n < a.grp; ++n) {
+          const float* t = p.page_ml +
+                           (((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + blk) * tpp * 2;
+          float m = -INFINITY;
+          for (int i = 0; i < tpp; ++i)
+            if (t[2 * i + 1] > 0.f) m = fmaxf(m, t[2 * i]);
+          if (m == -INFINITY) continue;
+          float l = 0.f;
+          for (int i = 0; i < tpp; ++i)
+            if (t[2 * i + 1] > 0.f) l += t[2 * i + 1] * __expf(t[2 * i] - m);
+          mass += __expf(fmaxf(m - s_M[n] * kLn2, -60.f)) * l / fmaxf(s_L[n], 1e-12f);
+        }
+      }
+      float* o = p.omega + (int64_t)unit * p.max_blocks + blk;
+      *o = *o * p.ema_beta + mass * one_minus;
+    }
+  }
+  if (blockIdx.y != 0) return;  // only the first CTA of a unit writes the attention output
   // pass 2: weights per chunk of rows, then threads over (head, dim)
   float o_acc[(8 * DH + 255) / 256];
 #pragma unroll
@@ -1069,6 +1113,8 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   SPHKV_REQUIRE(p.out || p.out_partial, SPHKV_E_ARG, "decode: out and out_partial both NULL");
   SPHKV_REQUIRE(p.rope_table == nullptr || p.positions != nullptr, SPHKV_E_ARG,
                 "decode: rope_table given without positions");
+  SPHKV_REQUIRE(p.omega == nullptr || p.page_ml != nullptr, SPHKV_E_ARG,
+                "decode: omega needs page_ml (the per-tile statistics it is computed from)");
   SPHKV_REQUIRE(p.dh == 64 || p.dh == 128, SPHKV_E_ARG, "decode: dh=%d (64 or 128)", p.dh);
   SPHKV_REQUIRE(p.B > 0 && p.Hkv > 0 && p.Hq > 0 && p.Hq % p.Hkv == 0, SPHKV_E_ARG,
                 "decode: B=%d Hq=%d Hkv=%d", p.B, p.Hq, p.Hkv);
@@ -1125,10 +1171,12 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
     rc = p.v_dtype == SPHKV_F16 ? launch_decode<64, __half>(a, smem_bytes, st)
                                 : launch_decode<64, __nv_bfloat16>(a, smem_bytes, st);
   if (rc) return rc;
+  // with an importance update, extra CTAs per unit share the walk over the blocks
+  const dim3 mgrid(a.n_units, p.omega ? (unsigned)min(16, (p.max_blocks + 255) / 256) : 1u);
   if (p.dh == 128)
-    merge_rows_kernel<128><<<a.n_units, 256, 0, st>>>(a);
+    merge_rows_kernel<128><<<mgrid, 256, 0, st>>>(a);
   else
-    merge_rows_kernel<64><<<a.n_units, 256, 0, st>>>(a);
+    merge_rows_kernel<64><<<mgrid, 256, 0, st>>>(a);
   return check_launch("merge_rows_kernel");
 }
 

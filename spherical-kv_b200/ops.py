@@ -109,18 +109,27 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
                  out_dtype: Optional[torch.dtype] = None, out_partial: Optional[torch.Tensor] = None,
                  page_ml: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
                  n_ctas: int = 0,
-                 want_out: bool = True) -> torch.Tensor:
+                 want_out: bool = True, omega: Optional[torch.Tensor] = None,
+                 ema_beta: float = 0.9) -> torch.Tensor:
     """One decode-attention step over the compressed cache.
 
     q: [B, Hq, dh] post-RoPE at the query position.  rope: table from rope_table() (None =
     keys are stored post-RoPE, no rotation).  Returns out [B, Hq, dh]; with `out_partial`
     ([B, Hq, dh+2] f32) the un-normalised (max, sum, acc) triple is written too.
     Numerics: spherical_kv_pipeline.py:2136-2177 with sm_scale = 1/sqrt(dh).
+    `omega` (f32 [B*Hkv, max_blocks]) is the page-importance EMA of
+    spherical_kv_pipeline.py:952-987, updated in place inside the merge kernel from the
+    per-tile statistics of this step; `page_ml` (f32 [B, Hq, max_blocks, page_size/16, 2]) is
+    allocated when omega is given without it.
     """
     lib = _lib.load()
     L = cache.lists
     B, Hq, dh = q.shape
-    _need_cuda(q, out, out_partial, page_ml, logits_out, rope)
+    if omega is not None and page_ml is None:
+        page_ml = torch.empty(B, Hq, L.max_blocks, L.page_size // 16, 2, dtype=torch.float32, device=q.device)
+    _need_cuda(q, out, out_partial, page_ml, logits_out, rope, omega)
+    if omega is not None:
+        assert omega.dtype == torch.float32 and omega.is_contiguous() and omega.numel() == B * L.Hkv * L.max_blocks
     assert B == L.B and dh == cache.dh
     if cache.scratch is None:
         cache.scratch = decode_scratch(cache, n_ctas)
@@ -138,6 +147,7 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     p.logits_out = _ptr(logits_out)
     p.scratch, p.scratch_bytes = cache.scratch.data_ptr(), cache.scratch.numel()
     p.status = cache.status.data_ptr()
+    p.omega, p.ema_beta = _ptr(omega), ema_beta
     p.B, p.Hq, p.Hkv, p.dh = B, Hq, L.Hkv, dh
     p.page_size, p.max_blocks, p.n_pages = L.page_size, L.max_blocks, L.n_pages
     p.max_pos = 0 if rope is None else rope.shape[0]

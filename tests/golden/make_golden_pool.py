@@ -1,4 +1,5 @@
-"""Generates `layer_pool.npz` by RUNNING THE REFERENCE's LayerPool (sphkv_lut.py) on the CPU.
+"""Generates `layer_pool.npz` and `omega_ema.npz` by RUNNING THE REFERENCE on the CPU:
+LayerPool (sphkv_lut.py) and _omega_ema_eager (spherical_kv_pipeline.py:952-987).
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden_pool.py
 
@@ -95,6 +96,26 @@ def main() -> None:
     path = os.path.join(HERE, "layer_pool.npz")
     np.savez_compressed(path, **out)
     print("layer_pool.npz", os.path.getsize(path), "bytes")
+
+    # ---- page-importance EMA: _omega_ema_eager on random block statistics ------------------
+    import spherical_kv_pipeline as skp
+    om = {}
+    for name, (num_kv, grp, max_blocks) in {"a": (2, 4, 37), "b": (8, 1, 5), "c": (3, 2, 130)}.items():
+        m = torch.randn(num_kv * grp, max_blocks, generator=gen) * 6.0
+        l = torch.rand(num_kv * grp, max_blocks, generator=gen) * 40.0
+        dead = torch.rand(num_kv * grp, max_blocks, generator=gen) < 0.2
+        l[dead] = 0.0
+        m[dead] = float("-inf")            # what a kernel leaves for an empty block
+        m[0, 0], l[0, 0] = 90.0, 1.0       # a dominant block: exercises the -60 clamp
+        if name == "b":
+            l[1], m[1] = 0.0, float("-inf")   # a head with no live block at all
+        prev = torch.rand(num_kv, max_blocks, generator=gen)
+        new = skp._omega_ema_eager(m, l, prev, num_kv, grp, max_blocks, 0.9)
+        om[f"{name}_m"], om[f"{name}_l"], om[f"{name}_prev"] = m.numpy(), l.numpy(), prev.numpy()
+        om[f"{name}_new"], om[f"{name}_shape"] = new.numpy(), np.array([num_kv, grp, max_blocks], np.int32)
+    path = os.path.join(HERE, "omega_ema.npz")
+    np.savez_compressed(path, **om)
+    print("omega_ema.npz", os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -268,3 +268,62 @@ def test_page_ml_side_output():
     live = torch.isfinite(m)
     assert torch.allclose(ml[..., 0][live], m[live], atol=1e-5, rtol=1e-5)
     assert torch.allclose(ml[..., 1][live], l[live], atol=1e-4, rtol=1e-4)
+
+
+def page_stats_from_logits(logits, max_blocks, N):
+    """per-block (max, sum) of every query head from the per-token logits (-inf = no token)"""
+    lg = logits.view(logits.shape[0] * logits.shape[1], max_blocks, N).cpu()
+    m = lg.max(-1).values
+    l = torch.exp(lg - torch.where(torch.isfinite(m), m, torch.zeros_like(m)).unsqueeze(-1)).sum(-1)
+    l = torch.where(torch.isfinite(m), l, torch.zeros_like(l))
+    return m, l
+
+
+@pytest.mark.parametrize("N", [16, 64])
+def test_tile_statistics_any_page_size(N):
+    """page_ml holds (max, sum) of every 16-token tile, (-inf, 0) for a tile without tokens"""
+    ctx, dh = 700, 128
+    cache, cbs, K, V, Q, _ = build(1, 8, 2, dh, ctx, N, pkg.REFERENCE_TIERS[:2], {1: 0.4, 2: 0.5})
+    L = cache.lists
+    table = pkg.rope_table(ctx + 8, dh, device=DEV)
+    tpp = N // 16
+    ml = torch.full((1, 8, L.max_blocks, tpp, 2), 7.0, device=DEV)
+    logits = torch.full((1, 8, L.max_blocks * N), float("-inf"), device=DEV)
+    pkg.decode_paged(Q.to(DEV), cache, table, page_ml=ml, logits_out=logits)
+    torch.cuda.synchronize()
+    m, l = page_stats_from_logits(logits, L.max_blocks * tpp, 16)
+    got = ml.view(8, L.max_blocks * tpp, 2).cpu()
+    nb = L.num_blocks.cpu()
+    for hq in range(8):
+        used = int(nb[hq // 4]) * tpp
+        live = torch.isfinite(m[hq, :used])
+        assert torch.allclose(got[hq, :used, 0][live], m[hq, :used][live], atol=1e-5, rtol=1e-5)
+        assert torch.allclose(got[hq, :used, 1][live], l[hq, :used][live], atol=1e-4, rtol=1e-4)
+        assert (got[hq, :used, 1][~live] == 0).all() and torch.isinf(got[hq, :used, 0][~live]).all()
+        assert (got[hq, used:] == 7.0).all()  # blocks beyond the list are not touched
+
+
+@pytest.mark.parametrize("N,B", [(16, 2), (64, 1), (64, 3)])
+def test_omega_ema_in_decode_epilogue(N, B):
+    """omega updated inside the merge kernel == _omega_ema_eager restatement applied to the
+    per-block statistics of the same step; two steps in a row accumulate"""
+    ctx, dh, Hq, Hkv = 900, 128, 8, 2
+    cache, cbs, K, V, Q, _ = build(B, Hq, Hkv, dh, ctx, N, pkg.REFERENCE_TIERS[:2], {1: 0.3, 2: 0.5}, seed=11)
+    L = cache.lists
+    table = pkg.rope_table(ctx + 8, dh, device=DEV)
+    g = torch.Generator().manual_seed(4)
+    omega0 = torch.rand(B * Hkv, L.max_blocks, generator=g)
+    omega = omega0.clone().to(DEV)
+    want = omega0
+    plain = pkg.decode_paged(Q.to(DEV), cache, table).clone()
+    for step in range(2):
+        q = (Q * (1.0 + 0.5 * step)).to(DEV)
+        logits = torch.full((B, Hq, L.max_blocks * N), float("-inf"), device=DEV)
+        out = pkg.decode_paged(q, cache, table, logits_out=logits, omega=omega, ema_beta=0.9)
+        torch.cuda.synchronize()
+        if step == 0:
+            # the side outputs do not change the attention result
+            assert torch.allclose(out.float(), plain.float(), rtol=1e-2, atol=1e-4)
+        m, l = page_stats_from_logits(logits, L.max_blocks, N)
+        want = orc.omega_ema(m, l, want, B * Hkv, Hq // Hkv, L.max_blocks, 0.9)
+        assert (omega.cpu() - want).abs().max().item() <= 2e-6, (step, (omega.cpu() - want).abs().max().item())

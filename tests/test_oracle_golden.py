@@ -175,3 +175,14 @@ def test_pool_append_bookkeeping_matches_reference():
     np.testing.assert_array_equal(bi.numpy(), z["bits_table1"])
     np.testing.assert_array_equal(ctx, z["ctx_lens1"])
     assert state["used"] == int(z["n_used1"]) and state["ctx"] == int(z["ctx1"])
+
+
+def test_omega_ema_matches_reference():
+    """oracle.omega_ema == _omega_ema_eager of the reference (dead blocks, a dominant block that
+    trips the -60 clamp, a head with no live block)"""
+    z = np.load(os.path.join(GOLDEN, "omega_ema.npz"))
+    for name in ("a", "b", "c"):
+        num_kv, grp, max_blocks = (int(x) for x in z[f"{name}_shape"])
+        got = orc.omega_ema(torch.from_numpy(z[f"{name}_m"]), torch.from_numpy(z[f"{name}_l"]),
+                            torch.from_numpy(z[f"{name}_prev"]), num_kv, grp, max_blocks, 0.9)
+        np.testing.assert_array_equal(got.numpy(), z[f"{name}_new"])
