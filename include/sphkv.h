@@ -97,6 +97,11 @@ typedef struct sphkv_encode_params {
   int64_t k_row_stride;     /* elements between consecutive source rows               */
   int64_t k_head_stride;    /* elements between consecutive heads of a row            */
   int64_t v_row_stride, v_head_stride;
+  /* code cache written by sphkv_encode_codes, read by sphkv_pages_from_codes only: per
+     tier slot s, radii f32 and centroid indices u8 laid out [Hkv][code_rows][dh / g_s]   */
+  const float* code_r[SPHKV_MAX_TIER_SLOTS];
+  const uint8_t* code_theta[SPHKV_MAX_TIER_SLOTS];
+  int64_t code_rows;
   int32_t n_bundles, n_pages, page_size, dh, Hkv;
   int32_t k_dtype, v_src_dtype, v_pool_dtype;
   int32_t radius_fmt;
@@ -105,6 +110,25 @@ typedef struct sphkv_encode_params {
 
 int64_t sphkv_encode_scratch_bytes(int32_t n_pages, int32_t page_size, int32_t dh);
 int sphkv_encode_pages(const sphkv_encode_params* p, void* stream);
+
+/* All-tier pre-encode: radius and nearest centroid of every (row, KV head, group) for every
+ * tier slot in ONE pass over the keys.  Replaces the per-tier loop of
+ * spherical_kv_pipeline.py:1535-1553 (three _encode_keys_with_codebooks calls per (layer,
+ * head), each re-reading K and recomputing the norms).  k_src as in sphkv_encode_params;
+ * r_out / theta_out are HOST arrays of tiers->n_slots device pointers, slot s receiving f32
+ * / u8 [Hkv][rows][dh / g_s] (a NULL pair skips that slot).  Values equal what
+ * sphkv_encode_pages computes for the same tier (same fixed fp32 order). */
+int sphkv_encode_codes(const void* k_src, int32_t k_dtype, int64_t k_row_stride,
+                       int64_t k_head_stride, int64_t rows, int32_t Hkv, int32_t dh,
+                       const float* codebooks, const sphkv_tiers* tiers, float* const* r_out,
+                       uint8_t* const* theta_out, void* stream);
+
+/* Re-paging without re-encoding: builds the byte pages (and V pages, when v_src is given) of
+ * the page lists in p from the code cache (p->code_r, p->code_theta, p->code_rows) instead of
+ * the keys; k_src, codebooks and scratch are ignored.  Replaces _rebuild_pages_for
+ * (spherical_kv_pipeline.py:2579-2660): index-select of cached codes + build_page_from_codes
+ * per page.  The pages are byte-identical to what sphkv_encode_pages writes from the keys. */
+int sphkv_pages_from_codes(const sphkv_encode_params* p, void* stream);
 
 /* ---- Decode ----------------------------------------------------------------------
  * Angle-domain decode attention over bit-packed pages with in-kernel back-rotation
@@ -244,6 +268,19 @@ int sphkv_pool_append_step(const float* k_post, const float* v_new, const float*
                            int32_t G, int32_t g, int32_t C, int32_t G_max, int32_t dh,
                            int32_t page_size, int32_t num_kv, int32_t max_blocks,
                            int32_t n_pool_pages, void* stream);
+
+/* ---- Codebook training inner loop ----------------------------------------------------
+ * Assignment + accumulation step of spherical_kmeans_gpu (codebooks/generate.py:47-58):
+ * sims = U @ centers^T, assigns = argmax (first maximum), sums = index_add of U by assigns,
+ * counts = bincount.  U f32 [N][d] (16-byte aligned), centers f32 [K][d], d in {8, 16, 32},
+ * K * d * 8 + 12 * K + 2052 <= 49152.  assigns i32 [N]; best_sim f32 [N] optional (the similarity of
+ * each point to its centre: sims.gather(1, assigns), used for the score at :71 and for
+ * re-seeding empty clusters at :61-64); sums f32 [K][d] and counts i32 [K] are zeroed and
+ * filled by the call.  Similarities use the encoder's fixed fp32 fma order; the order of
+ * the float additions into sums is not fixed, as with index_add_ on a GPU. */
+int sphkv_kmeans_assign(const float* U, int64_t N, int32_t d, const float* centers, int32_t K,
+                        int32_t* assigns, float* best_sim, float* sums, int32_t* counts,
+                        void* stream);
 
 /* Implements the launcher new_fused_decode.cpp:3-22 declares and the reference never
  * defines: logits from a q.centroid table.  q_lut f32 [Hq][num_tiers][G_max][cb_size_max];

@@ -440,3 +440,37 @@ def pool_append_bookkeeping(state: dict, block_table, bits_table, pids, num_kv: 
             pids[h] = start + h
     state["ctx"] = cur + 1
     return slot, is_new
+
+
+def kmeans_step(U: torch.Tensor, centers: torch.Tensor):
+    """One iteration body of spherical_kmeans_gpu (codebooks/generate.py:47-66) on the CPU.
+    Returns (assigns, best_sim, sums, counts, next_centers)."""
+    sims = U @ centers.T
+    assigns = sims.argmax(dim=1)
+    sums = torch.zeros_like(centers)
+    sums.index_add_(0, assigns, U)
+    counts = torch.bincount(assigns, minlength=centers.shape[0])
+    new_c = sums / counts.float().clamp(min=1).unsqueeze(1)
+    best = sims.gather(1, assigns.unsqueeze(1)).squeeze(1)
+    # The reference tests for empty clusters on the counts AFTER clamping them to >= 1
+    # (generate.py:56-60), so its re-seeding branch never runs: an empty cluster's centre
+    # becomes the zero vector (normalize(0) = 0).  Restated as it behaves.
+    return assigns, best, sums, counts, torch.nn.functional.normalize(new_c, dim=1)
+
+
+def spherical_kmeans(U: torch.Tensor, K: int, niter: int, init_centers: torch.Tensor):
+    """spherical_kmeans_gpu (codebooks/generate.py:31-75) for given starting centres
+    [nredo, K, d]: iterate to convergence or niter, score = mean best similarity, keep the
+    best restart.  Returns (centers, score)."""
+    best_centers, best_score = None, -1e9
+    for redo in range(init_centers.shape[0]):
+        centers, prev = init_centers[redo].clone(), None
+        for _ in range(niter):
+            assigns, _, _, _, nxt = kmeans_step(U, centers)
+            if prev is not None and torch.equal(assigns, prev):
+                break
+            prev, centers = assigns, nxt
+        score = (U @ centers.T).max(dim=1).values.mean().item()
+        if score > best_score:
+            best_score, best_centers = score, centers.clone()
+    return best_centers, best_score

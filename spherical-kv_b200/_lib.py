@@ -34,6 +34,8 @@ class EncodeParams(C.Structure):
         ("v_pool", C.c_void_p), ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64),
         ("k_row_stride", C.c_int64), ("k_head_stride", C.c_int64),
         ("v_row_stride", C.c_int64), ("v_head_stride", C.c_int64),
+        ("code_r", C.c_void_p * MAX_TIER_SLOTS), ("code_theta", C.c_void_p * MAX_TIER_SLOTS),
+        ("code_rows", C.c_int64),
         ("n_bundles", C.c_int32), ("n_pages", C.c_int32), ("page_size", C.c_int32),
         ("dh", C.c_int32), ("Hkv", C.c_int32),
         ("k_dtype", C.c_int32), ("v_src_dtype", C.c_int32), ("v_pool_dtype", C.c_int32),
@@ -66,6 +68,10 @@ SIGNATURES = {
     "sphkv_struct_size": (C.c_int, [C.c_int]),
     "sphkv_rope_table_build": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "sphkv_encode_pages": (C.c_int, [C.POINTER(EncodeParams), C.c_void_p]),
+    "sphkv_pages_from_codes": (C.c_int, [C.POINTER(EncodeParams), C.c_void_p]),
+    "sphkv_encode_codes": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+                                     C.c_void_p, C.POINTER(Tiers), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                     C.c_void_p]),
     "sphkv_encode_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32]),
     "sphkv_decode_scratch_bytes": (C.c_int64, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "sphkv_decode_paged": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),
@@ -82,6 +88,7 @@ SIGNATURES = {
     "sphkv_ragged_logits": (C.c_int, [C.c_void_p] * 9 + [C.c_int32] * 12 + [C.c_void_p]),
     "sphkv_pool_build_pages": (C.c_int, [C.c_void_p] * 3 + [C.c_int32, C.c_int64, C.c_int64, C.c_void_p,
                                          C.c_int32] + [C.c_void_p] * 4 + [C.c_int32] * 3 + [C.c_void_p]),
+    "sphkv_kmeans_assign": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32] + [C.c_void_p] * 5),
     "sphkv_pool_append_step": (C.c_int, [C.c_void_p] * 12 + [C.c_int32] * 10 + [C.c_void_p]),
 }
 

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_PATH = os.path.join(HERE, "libsphkv_b200.so")
-SOURCES = ["capi.cu", "decode.cu", "encode.cu", "compat.cu", "pool.cu"]
+SOURCES = ["capi.cu", "decode.cu", "encode.cu", "compat.cu", "pool.cu", "kmeans.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC,

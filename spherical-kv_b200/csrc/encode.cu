@@ -67,6 +67,8 @@ constexpr int kMaxBundlesPerCta = 8;  // consecutive bundles one CTA walks (they
 // search only, results to the scratch arrays r[(page*N + slot) * (dh/16) + group] (f32) and
 // theta[...] (u8).  PHASE 2: page assembly + V pages from those arrays.  Splitting lets the
 // FMA-bound search run without the barriers and small dependent loads of the page bookkeeping.
+// PHASE 3: page assembly from a per-token code cache (sphkv_encode_codes) gathered through
+// src_index: re-paging after a tier change without touching the dense keys.
 template <int GS, int PHASE>
 __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const EncodeArgs a) {
   const sphkv_encode_params& p = a.p;
@@ -78,7 +80,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   const int G = dh / GS, g_shift = 31 - __clz(G);
   const int n_shift = 31 - __clz(N);  // page_size is a power of two
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-  const int C_cap = PHASE == 2 ? 0 : p.tiers.C_max;
+  const int C_cap = PHASE >= 2 ? 0 : p.tiers.C_max;
   const int GST = dh >> 4;  // group stride of the scratch arrays
   float* scr_r = reinterpret_cast<float*>(p.scratch);
   uint8_t* scr_t = reinterpret_cast<uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     const int img_stride = ((8 + 4 * G + (N * G * bits + 7) / 8 + N * G * rb) + 15) & ~15;
 
     // ---- codebook of (head, slot) -> shared memory, 128-bit copies ---------------------------
-    if (PHASE != 2 && head * p.tiers.n_slots + slot != loaded_key) {
+    if (PHASE < 2 && head * p.tiers.n_slots + slot != loaded_key) {
       const float4* src = reinterpret_cast<const float4*>(
           p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
                             p.tiers.g_max);
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     }
 
     // ---- radius + nearest centroid: warp = group, lane = token slots lane + 32 h, h < 4 ----
-    if (PHASE != 2 && warp < G) {
+    if (PHASE < 2 && warp < G) {
       const float* cbg = cb_s + (warp << bits) * GS;
       float k[4][GS];
       bool have[4];
@@ -215,6 +217,27 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
           const int64_t si = ((int64_t)page * N + tin) * GST + gq;
           rv = scr_r[si];
           tv = scr_t[si];
+        }
+        r_s[i] = rv;
+        th_s[i] = tv;
+      }
+    }
+    if (PHASE == 3) {
+      const float* cr = p.code_r[slot];
+      const uint8_t* ct = p.code_theta[slot];
+      for (int i = threadIdx.x; i < TB * G; i += blockDim.x) {
+        const int ts = i >> g_shift, gq = i & (G - 1);
+        const int q = ts >> n_shift, tin = ts & (N - 1);
+        const int page = page_s[q];
+        float rv = 0.f;
+        uint8_t tv = 0;
+        if (page >= 0) {
+          const int64_t row = p.src_index[(int64_t)page * N + tin];
+          if (row >= 0) {
+            const int64_t ci = ((int64_t)head * p.code_rows + row) * G + gq;
+            rv = cr[ci];
+            tv = ct[ci];
+          }
         }
         r_s[i] = rv;
         th_s[i] = tv;
@@ -365,6 +388,136 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   }
 }
 
+// ---- all-tier code cache ---------------------------------------------------------------------
+// Radius and nearest centroid of every (token, KV head, group) for EVERY tier slot in one pass
+// over the keys (the pre-encode of spherical_kv_pipeline.py:1535-1553, which calls
+// _encode_keys_with_codebooks once per tier).  A thread holds four tokens' 32-dim slice; the two
+// 16-dim halves serve the g = 16 tiers, the whole slice the g = 32 tiers, and the squared norm
+// of the 32-dim group continues the fma chain of its first half, so every value equals what
+// the per-tier encoder computes (same fixed order).  Output per slot s, head-major like the
+// reference's per-(layer, head) cache: r[s][head][row][G_s] f32, theta[s][head][row][G_s] u8.
+struct CodesArgs {
+  const void* k_src;
+  const float* codebooks;
+  float* r_out[SPHKV_MAX_TIER_SLOTS];
+  uint8_t* th_out[SPHKV_MAX_TIER_SLOTS];
+  int64_t k_row_stride, k_head_stride, rows;
+  int k_dtype, dh;
+  int cb_off[SPHKV_MAX_TIER_SLOTS];  // float offset of each slot's staged codebook
+  sphkv_tiers tiers;
+};
+
+template <int OFF, int GS>
+__device__ __forceinline__ void search_slice(const float (&k)[4][32], const float* __restrict__ cbg, int C,
+                                             int (&code)[4]) {
+  float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int h = 0; h < 4; ++h) code[h] = 0;
+  for (int c = 0; c < C; ++c) {
+    const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < GS / 4; ++i) {
+      const float4 v = row[i];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        sacc[h] = __fmaf_rn(k[h][OFF + 4 * i], v.x, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][OFF + 4 * i + 1], v.y, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][OFF + 4 * i + 2], v.z, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][OFF + 4 * i + 3], v.w, sacc[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+      if (sacc[h] > best[h]) { best[h] = sacc[h]; code[h] = c; }
+  }
+}
+
+__global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* cb_s = reinterpret_cast<float*>(smem);
+  const int head = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G32 = a.dh >> 5;                  // 32-dim groups per head: 2 or 4
+  const int grp = warp % G32, set = warp / G32;
+  const int sets = (kEncThreads / 32) / G32;  // token sets of 128 per CTA
+  // stage every slot's codebook of this head: [G_s][C_s][g_s] packed
+  for (int s = 0; s < a.tiers.n_slots; ++s) {
+    const int gs = a.tiers.g[s], bits = a.tiers.bits[s], G = a.dh / gs, q4n = gs >> 2;
+    const float4* src = reinterpret_cast<const float4*>(
+        a.codebooks + ((int64_t)(head * a.tiers.n_slots + s) * a.tiers.G_max) * a.tiers.C_max * a.tiers.g_max);
+    float4* dst = reinterpret_cast<float4*>(cb_s + a.cb_off[s]);
+    const int total = (G << bits) * q4n, row_stride4 = a.tiers.g_max >> 2;
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+      const int q4 = i % q4n, row = i / q4n;
+      dst[i] = __ldg(src + ((int64_t)(row >> bits) * a.tiers.C_max + (row & ((1 << bits) - 1))) * row_stride4 + q4);
+    }
+  }
+  __syncthreads();
+
+  const int64_t row0 = ((int64_t)blockIdx.x * sets + set) * 128;
+  float k[4][32];
+  bool have[4];
+#pragma unroll
+  for (int h = 0; h < 4; ++h) {
+    const int64_t row = row0 + lane + 32 * h;
+    have[h] = row < a.rows;
+    if (have[h]) {
+      load_group<32>(a.k_src, a.k_dtype, row * a.k_row_stride + (int64_t)head * a.k_head_stride + grp * 32, k[h]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) k[h][i] = 0.f;
+    }
+  }
+  float na[4] = {0.f, 0.f, 0.f, 0.f}, nb[4] = {0.f, 0.f, 0.f, 0.f}, nab[4];
+#pragma unroll
+  for (int d = 0; d < 16; ++d)
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      na[h] = __fmaf_rn(k[h][d], k[h][d], na[h]);
+      nb[h] = __fmaf_rn(k[h][16 + d], k[h][16 + d], nb[h]);
+    }
+#pragma unroll
+  for (int h = 0; h < 4; ++h) nab[h] = na[h];
+#pragma unroll
+  for (int d = 16; d < 32; ++d)
+#pragma unroll
+    for (int h = 0; h < 4; ++h) nab[h] = __fmaf_rn(k[h][d], k[h][d], nab[h]);
+
+  for (int s = 0; s < a.tiers.n_slots; ++s) {
+    if (a.r_out[s] == nullptr) continue;
+    const int bits = a.tiers.bits[s], C = 1 << bits;
+    int code[4];
+    if (a.tiers.g[s] == 16) {
+      const int G = a.dh >> 4;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int gam = 2 * grp + half;
+        if (half == 0)
+          search_slice<0, 16>(k, cb_s + a.cb_off[s] + (gam << bits) * 16, C, code);
+        else
+          search_slice<16, 16>(k, cb_s + a.cb_off[s] + (gam << bits) * 16, C, code);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          if (!have[h]) continue;
+          const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G + gam;
+          a.r_out[s][o] = __fsqrt_rn(half == 0 ? na[h] : nb[h]);
+          a.th_out[s][o] = (uint8_t)code[h];
+        }
+      }
+    } else {
+      search_slice<0, 32>(k, cb_s + a.cb_off[s] + (grp << bits) * 32, C, code);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (!have[h]) continue;
+        const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G32 + grp;
+        a.r_out[s][o] = __fsqrt_rn(nab[h]);
+        a.th_out[s][o] = (uint8_t)code[h];
+      }
+    }
+  }
+}
+
 // ---- RoPE table ------------------------------------------------------------------------------
 // row(pos)[(s*4 + j)*8 + e]     = cos(float(pos) * inv_freq[f]),
 // row(pos)[(s*4 + j)*8 + 4 + e] = sin(...),  f = 16 s + 2 j + (e & 1) + 8 (e >> 1).
@@ -405,8 +558,12 @@ extern "C" int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh,
 }
 
 template <int GS>
-static int launch_encode(const EncodeArgs& a, bool split, int smem_bytes, cudaStream_t st) {
+static int launch_encode(const EncodeArgs& a, bool split, bool from_codes, int smem_bytes, cudaStream_t st) {
   const int grid = (a.p.n_bundles + a.bundles_per_cta - 1) / a.bundles_per_cta;
+  if (from_codes) {
+    encode_bundle_kernel<GS, 3><<<grid, kEncThreads, smem_bytes, st>>>(a);
+    return check_launch("encode_bundle_kernel<from codes>");
+  }
   if (split) {
     encode_bundle_kernel<GS, 1><<<grid, kEncThreads, smem_bytes, st>>>(a);
     if (int rc = check_launch("encode_bundle_kernel<search>")) return rc;
@@ -422,13 +579,20 @@ extern "C" int64_t sphkv_encode_scratch_bytes(int32_t n_pages, int32_t page_size
   return ((int64_t)n_pages * page_size * (dh / 16) * 5 + 15) / 16 * 16;
 }
 
-extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
+static int encode_impl(const sphkv_encode_params* pp, void* stream, bool from_codes) {
   SPHKV_REQUIRE(pp != nullptr, SPHKV_E_ARG, "encode: params is NULL");
   const sphkv_encode_params& p = *pp;
   if (p.n_bundles == 0) return 0;
-  SPHKV_REQUIRE(p.k_src && p.src_index && p.bundles && p.page_head && p.page_slot && p.ptable &&
-                    p.codebooks && p.k_pages,
+  SPHKV_REQUIRE(p.src_index && p.bundles && p.page_head && p.page_slot && p.ptable && p.k_pages,
                 SPHKV_E_ARG, "encode: a required pointer is NULL");
+  if (from_codes) {
+    SPHKV_REQUIRE(p.code_rows > 0, SPHKV_E_ARG, "pages_from_codes: code_rows=%lld", (long long)p.code_rows);
+    for (int s = 0; s < p.tiers.n_slots && s < SPHKV_MAX_TIER_SLOTS; ++s)
+      SPHKV_REQUIRE(p.code_r[s] && p.code_theta[s], SPHKV_E_ARG,
+                    "pages_from_codes: code cache of tier slot %d is NULL", s);
+  } else {
+    SPHKV_REQUIRE(p.k_src && p.codebooks, SPHKV_E_ARG, "encode: k_src / codebooks is NULL");
+  }
   SPHKV_REQUIRE(p.n_bundles > 0 && p.n_pages > 0, SPHKV_E_ARG, "encode: n_bundles=%d n_pages=%d",
                 p.n_bundles, p.n_pages);
   SPHKV_REQUIRE(p.dh == 64 || p.dh == 128, SPHKV_E_ARG, "encode: dh=%d (64 or 128)", p.dh);
@@ -442,7 +606,7 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
                 "encode: radius_fmt=%d", p.radius_fmt);
   SPHKV_REQUIRE(((uintptr_t)p.k_pages & 3) == 0, SPHKV_E_ALIGN, "encode: k_pages needs 4 B alignment");
   if (int rc = validate_tiers(p.tiers, p.dh)) return rc;
-  SPHKV_REQUIRE(((uintptr_t)p.codebooks & 15) == 0 && (p.tiers.g_max & 3) == 0 &&
+  SPHKV_REQUIRE((from_codes || ((uintptr_t)p.codebooks & 15) == 0) && (p.tiers.g_max & 3) == 0 &&
                     ((uintptr_t)p.v_pool & 15) == 0,
                 SPHKV_E_ALIGN, "encode: codebooks / v_pool need 16 B alignment, g_max a multiple of 4");
   // shared memory: codebook of the widest tier + staging + page images
@@ -481,6 +645,7 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
     set((const void*)encode_bundle_kernel<16, 0>); set((const void*)encode_bundle_kernel<16, 1>);
     set((const void*)encode_bundle_kernel<16, 2>); set((const void*)encode_bundle_kernel<32, 0>);
     set((const void*)encode_bundle_kernel<32, 1>); set((const void*)encode_bundle_kernel<32, 2>);
+    set((const void*)encode_bundle_kernel<16, 3>); set((const void*)encode_bundle_kernel<32, 3>);
     if (e != cudaSuccess) {
       set_error("encode: cudaFuncSetAttribute(%d B): %s", smem_bytes, cudaGetErrorString(e));
       return (int)e;
@@ -491,10 +656,64 @@ extern "C" int sphkv_encode_pages(const sphkv_encode_params* pp, void* stream) {
   bool any16 = false, any32 = false;
   for (int s = 0; s < p.tiers.n_slots; ++s) (p.tiers.g[s] == 16 ? any16 : any32) = true;
   if (any16) {
-    if (int rc = launch_encode<16>(a, split, smem_bytes, st)) return rc;
+    if (int rc = launch_encode<16>(a, split, from_codes, smem_bytes, st)) return rc;
   }
   if (any32) {
-    if (int rc = launch_encode<32>(a, split, smem_bytes, st)) return rc;
+    if (int rc = launch_encode<32>(a, split, from_codes, smem_bytes, st)) return rc;
   }
   return 0;
+}
+
+extern "C" int sphkv_encode_pages(const sphkv_encode_params* p, void* stream) {
+  return encode_impl(p, stream, false);
+}
+
+extern "C" int sphkv_pages_from_codes(const sphkv_encode_params* p, void* stream) {
+  return encode_impl(p, stream, true);
+}
+
+extern "C" int sphkv_encode_codes(const void* k_src, int32_t k_dtype, int64_t k_row_stride,
+                                  int64_t k_head_stride, int64_t rows, int32_t Hkv, int32_t dh,
+                                  const float* codebooks, const sphkv_tiers* tiers, float* const* r_out,
+                                  uint8_t* const* theta_out, void* stream) {
+  SPHKV_REQUIRE(k_src && codebooks && tiers && r_out && theta_out, SPHKV_E_ARG, "encode_codes: NULL pointer");
+  SPHKV_REQUIRE(rows >= 0 && Hkv > 0 && (dh == 64 || dh == 128) && k_dtype >= 0 && k_dtype <= 2, SPHKV_E_ARG,
+                "encode_codes: rows=%lld Hkv=%d dh=%d k_dtype=%d", (long long)rows, Hkv, dh, k_dtype);
+  if (int rc = validate_tiers(*tiers, dh)) return rc;
+  SPHKV_REQUIRE(((uintptr_t)codebooks & 15) == 0 && (tiers->g_max & 3) == 0, SPHKV_E_ALIGN,
+                "encode_codes: codebooks need 16 B alignment, g_max a multiple of 4");
+  if (rows == 0) return 0;
+  CodesArgs a;
+  a.k_src = k_src; a.codebooks = codebooks;
+  a.k_row_stride = k_row_stride; a.k_head_stride = k_head_stride; a.rows = rows;
+  a.k_dtype = k_dtype; a.dh = dh; a.tiers = *tiers;
+  int off = 0;
+  bool any = false;
+  for (int s = 0; s < SPHKV_MAX_TIER_SLOTS; ++s) {
+    a.r_out[s] = s < tiers->n_slots ? r_out[s] : nullptr;
+    a.th_out[s] = s < tiers->n_slots ? theta_out[s] : nullptr;
+    a.cb_off[s] = off;
+    if (s < tiers->n_slots) {
+      SPHKV_REQUIRE((a.r_out[s] == nullptr) == (a.th_out[s] == nullptr), SPHKV_E_ARG,
+                    "encode_codes: slot %d needs both r_out and theta_out (or neither)", s);
+      any = any || a.r_out[s] != nullptr;
+      off += dh << tiers->bits[s];  // G_s * C_s * g_s floats
+    }
+  }
+  SPHKV_REQUIRE(any, SPHKV_E_ARG, "encode_codes: no output requested");
+  const int smem_bytes = off * 4;
+  SPHKV_REQUIRE(smem_bytes <= 200 * 1024, SPHKV_E_LIMIT, "encode_codes: codebooks need %d B of shared memory", smem_bytes);
+  static int configured = 0;
+  if (configured < smem_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(encode_codes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) {
+      set_error("encode_codes: cudaFuncSetAttribute(%d B): %s", smem_bytes, cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = smem_bytes;
+  }
+  const int sets = (kEncThreads / 32) / (dh >> 5);
+  const dim3 grid((unsigned)((rows + sets * 128 - 1) / (sets * 128)), (unsigned)Hkv);
+  encode_codes_kernel<<<grid, kEncThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch("encode_codes_kernel");
 }

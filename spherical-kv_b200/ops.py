@@ -95,6 +95,71 @@ def encode_pages(k_src: torch.Tensor, v_src: Optional[torch.Tensor], lists: Page
     return out
 
 
+class CodeCache:
+    """Per-token codes of every tier (the reference's `_codes_all`, spherical_kv_pipeline.py:
+    1535-1553): r[s] f32 and theta[s] u8, both [Hkv, rows, dh / g_s], for tier slot s."""
+
+    def __init__(self, r, theta, rows: int, tiers: TierSet):
+        self.r, self.theta, self.rows, self.tiers = r, theta, rows, tiers
+
+
+def encode_codes(k_src: torch.Tensor, codebooks: torch.Tensor, tiers: TierSet) -> CodeCache:
+    """One pass over [rows, Hkv, dh] keys -> codes of ALL tier slots (one K read, shared norms);
+    replaces the three per-tier encodes of spherical_kv_pipeline.py:1538-1552."""
+    lib = _lib.load()
+    _need_cuda(k_src, codebooks)
+    rows, hkv, dh = k_src.shape
+    assert dh == tiers.dh
+    dev = k_src.device
+    r = [torch.empty(hkv, rows, dh // t.g, dtype=torch.float32, device=dev) for t in tiers.tiers]
+    th = [torch.empty(hkv, rows, dh // t.g, dtype=torch.uint8, device=dev) for t in tiers.tiers]
+    n = len(tiers.tiers)
+    r_ptrs = (C.c_void_p * n)(*[x.data_ptr() for x in r])
+    t_ptrs = (C.c_void_p * n)(*[x.data_ptr() for x in th])
+    ct = tiers.to_c()
+    _lib.check(lib.sphkv_encode_codes(k_src.data_ptr(), _DT[k_src.dtype], k_src.stride(0), k_src.stride(1), rows,
+                                      hkv, dh, codebooks.data_ptr(), C.byref(ct), r_ptrs, t_ptrs, _stream()),
+               "sphkv_encode_codes")
+    return CodeCache(r, th, rows, tiers)
+
+
+def pages_from_codes(codes: CodeCache, v_src: Optional[torch.Tensor], lists: PageLists,
+                     codebooks: torch.Tensor, radius_fmt: int = _lib.RADIUS_I8,
+                     v_dtype: torch.dtype = torch.float16, out: Optional[PagedCache] = None) -> PagedCache:
+    """Builds the pages `lists` describes from cached codes instead of the keys: re-tiering
+    without re-encoding (_rebuild_pages_for, spherical_kv_pipeline.py:2579-2660).  `codebooks`
+    is only recorded in the returned cache (decode needs it); no key or codebook is read."""
+    lib = _lib.load()
+    tiers = codes.tiers
+    _need_cuda(v_src, lists.src_index, lists.bundles, lists.ptable, *codes.r, *codes.theta)
+    hkv, dh = lists.Hkv, tiers.dh
+    dev = codes.r[0].device
+    if out is None:
+        k_pages = torch.zeros(lists.pool_bytes, dtype=torch.uint8, device=dev)
+        v_pool = torch.zeros(lists.n_pages, lists.page_size, dh, dtype=v_dtype, device=dev)
+        out = PagedCache(tiers=tiers, lists=lists, codebooks=codebooks, k_pages=k_pages,
+                         v_pool=v_pool, radius_fmt=radius_fmt)
+    p = _lib.EncodeParams()
+    p.v_src = _ptr(v_src)
+    p.src_index, p.bundles = lists.src_index.data_ptr(), lists.bundles.data_ptr()
+    p.page_head, p.page_slot = lists.page_head.data_ptr(), lists.page_slot.data_ptr()
+    p.ptable = lists.ptable.data_ptr()
+    p.k_pages, p.v_pool = out.k_pages.data_ptr(), out.v_pool.data_ptr()
+    for s in range(len(tiers.tiers)):
+        p.code_r[s], p.code_theta[s] = codes.r[s].data_ptr(), codes.theta[s].data_ptr()
+    p.code_rows = codes.rows
+    if v_src is not None:
+        p.v_row_stride, p.v_head_stride = v_src.stride(0), v_src.stride(1)
+        p.v_src_dtype = _DT[v_src.dtype]
+    p.n_bundles, p.n_pages = lists.bundles.shape[0], lists.n_pages
+    p.page_size, p.dh, p.Hkv = lists.page_size, dh, hkv
+    p.v_pool_dtype = _DT[out.v_pool.dtype]
+    p.radius_fmt = radius_fmt
+    p.tiers = tiers.to_c()
+    _lib.check(lib.sphkv_pages_from_codes(C.byref(p), _stream()), "sphkv_pages_from_codes")
+    return out
+
+
 def decode_scratch(cache: PagedCache, n_ctas: int = 0) -> torch.Tensor:
     lib = _lib.load()
     L = cache.lists

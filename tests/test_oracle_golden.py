@@ -186,3 +186,17 @@ def test_omega_ema_matches_reference():
         got = orc.omega_ema(torch.from_numpy(z[f"{name}_m"]), torch.from_numpy(z[f"{name}_l"]),
                             torch.from_numpy(z[f"{name}_prev"]), num_kv, grp, max_blocks, 0.9)
         np.testing.assert_array_equal(got.numpy(), z[f"{name}_new"])
+
+
+def test_kmeans_restatement_matches_reference():
+    """oracle.spherical_kmeans from the reference's own starting centres == the reference's
+    spherical_kmeans_gpu result (two restarts, early convergence, N < K padding)"""
+    z = np.load(os.path.join(GOLDEN, "kmeans.npz"))
+    for name in ("g16", "g32", "tiny"):
+        N, d, K, niter, nredo = (int(x) for x in z[f"{name}_cfg"])
+        U = torch.from_numpy(z[f"{name}_U"])
+        if N < K:
+            U = U.repeat((K + N - 1) // N, 1)[:K]
+        centers, score = orc.spherical_kmeans(U, K, niter, torch.from_numpy(z[f"{name}_init"]))
+        np.testing.assert_array_equal(centers.numpy(), z[f"{name}_centers"])
+        assert score == float(z[f"{name}_score"])
