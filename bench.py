@@ -254,7 +254,7 @@ def run_side_workload(args) -> None:
                                                      f"log-sum-exp merge; {n_seq} sequences cycled (L2)"},
                               "cuda_graph": graphed, "algorithmic_bytes_total": alg,
                               "achieved_hbm_gbs_all_gpus": alg / (ms * 1e-3) / 1e9}), flush=True)
-    else:  # encode
+    elif args.workload == "encode":
         ctx, layers = args.ctx, min(args.layers, 8)
         assign1 = torch.full((1, Hkv, ctx), 1, dtype=torch.uint8, device=dev)
         assign2 = torch.full((1, Hkv, ctx), 2, dtype=torch.uint8, device=dev)
@@ -285,6 +285,137 @@ def run_side_workload(args) -> None:
                                                      f"tier-1 (C=64) and tier-2 (C=16) pages for every token"},
                               "gmac_per_s": th * (dh // 16) * 16 * 80 / (ms * 1e-3) / 1e9,
                               "hbm_gbs": (rd + wr) / (ms * 1e-3) / 1e9}), flush=True)
+    elif args.workload == "recode":
+        # all-tier code cache in one pass over K, then re-paging from it, against the per-tier route
+        ctx, layers = args.ctx, min(args.layers, 4)
+        specs3 = pkg.REFERENCE_TIERS
+        tiers3 = pkg.TierSet(dh, specs3)
+        cb3 = tiers3.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs3, seed=9)])
+        Ks = [(torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale) for _ in range(layers)]
+        Vs = [k.bfloat16() for k in Ks]
+        per_tier = [pkg.build_page_lists(torch.full((1, Hkv, ctx), t.tier_id, dtype=torch.uint8, device=dev),
+                                         tiers3, N) for t in specs3]
+        mixed = pkg.build_page_lists(pkg.synth.make_tier_assign(1, Hkv, ctx, {1: 0.2, 2: 0.5, 3: 0.3}, seed=1,
+                                                                per_head=True).to(dev), tiers3, N)
+        codes = pkg.encode_codes(Ks[0], cb3, tiers3)
+        outs = [pkg.encode_pages(Ks[0], None, l, cb3, tiers3) for l in per_tier]
+        direct = pkg.encode_pages(Ks[0], Vs[0], mixed, cb3, tiers3, v_dtype=torch.bfloat16)
+        again = pkg.pages_from_codes(codes, Vs[0], mixed, cb3, v_dtype=torch.bfloat16)
+        same = bool(torch.equal(direct.k_pages, again.k_pages) and torch.equal(direct.v_pool, again.v_pool))
+
+        def one_pass():
+            for Kt in Ks:
+                pkg.encode_codes(Kt, cb3, tiers3)
+
+        def three_passes():
+            for Kt in Ks:
+                for l, o in zip(per_tier, outs):
+                    pkg.encode_pages(Kt, None, l, cb3, tiers3, out=o)
+
+        def repage():
+            for Vt in Vs:
+                pkg.pages_from_codes(codes, Vt, mixed, cb3, out=again)
+
+        def reencode():
+            for Kt, Vt in zip(Ks, Vs):
+                pkg.encode_pages(Kt, Vt, mixed, cb3, tiers3, out=direct)
+
+        res = {}
+        for name, fn in (("codes_one_pass", one_pass), ("encode_three_tiers", three_passes),
+                         ("repage_from_codes", repage), ("reencode_from_keys", reencode)):
+            for _ in range(args.warmup):
+                fn()
+            res[name] = ev_time(fn, args.steps)
+        th = layers * ctx * Hkv
+        if rank == 0:
+            print(json.dumps({"metric": "all_tier_codes_token_heads_per_s", "value": th / (res["codes_one_pass"] * 1e-3),
+                              "unit": "token-heads/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                              "ms_per_step": res["codes_one_pass"], "higher_is_better": True, "data": "synthetic",
+                              "config": {"workload": f"codes of tiers 1/2/3 for {ctx} tokens x {layers} layers x {Hkv} KV "
+                                                     f"heads x dh {dh} in one pass over fp32 K; re-paging a 20/50/30 "
+                                                     f"tier mix from the cache ({N}-token pages, bf16 V)"},
+                              "ms": res, "speedup_vs_three_encodes": res["encode_three_tiers"] / res["codes_one_pass"],
+                              "repage_speedup_vs_reencode": res["reencode_from_keys"] / res["repage_from_codes"],
+                              "repage_bytes_identical": same,
+                              "gmac_per_s": th * dh * (64 + 16 + 8) / (res["codes_one_pass"] * 1e-3) / 1e9}), flush=True)
+    elif args.workload == "kmeans":
+        import torch.nn.functional as F
+        res = []
+        for Np, d, K in ((4_000_000, 16, 64), (4_000_000, 16, 16), (2_000_000, 32, 8)):
+            U = F.normalize(torch.randn(Np, d, generator=gen, device=dev), dim=1)
+            Cn = F.normalize(torch.randn(K, d, generator=gen, device=dev), dim=1)
+
+            def torch_step():
+                sims = U @ Cn.T
+                a_ = sims.argmax(1)
+                torch.zeros_like(Cn).index_add_(0, a_, U)
+                torch.bincount(a_, minlength=K)
+
+            for _ in range(args.warmup):
+                pkg.kmeans_assign(U, Cn, want_sim=False); torch_step()
+            t_k = ev_time(lambda: pkg.kmeans_assign(U, Cn, want_sim=False), args.steps)
+            t_t = ev_time(torch_step, args.steps)
+            res.append({"N": Np, "d": d, "K": K, "kernel_us": t_k * 1e3, "torch_ops_us": t_t * 1e3,
+                        "points_per_s": Np / (t_k * 1e-3), "tmac_per_s": Np * K * d / (t_k * 1e-3) / 1e12,
+                        "read_gbs": Np * d * 4 / (t_k * 1e-3) / 1e9})
+        if rank == 0:
+            print(json.dumps({"metric": "kmeans_assign_points_per_s", "value": res[0]["points_per_s"], "unit": "points/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                              "data": "synthetic",
+                              "config": {"workload": "spherical k-means assignment + accumulation step (codebook "
+                                                     "training inner loop) on random unit vectors; torch_ops = the "
+                                                     "same step as matmul + argmax + index_add_ + bincount"},
+                              "cases": res}), flush=True)
+    else:  # pool: device-resident LayerPool
+        import time as _time
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "spherical-kv_b200", "dropin"))
+        import sphkv_lut
+        from types import SimpleNamespace
+        ctx, Np = min(args.ctx, 32768), 16
+        tobj = [SimpleNamespace(tier_id=0, g=dh, G=1, b_theta=0)] + [
+            SimpleNamespace(tier_id=t.tier_id, g=t.g, G=dh // t.g, b_theta=t.b_theta) for t in pkg.REFERENCE_TIERS]
+        idx_map = sphkv_lut.make_tier_idx_map(tobj)
+        cpu_gen = torch.Generator().manual_seed(5)
+        per_head, cbs = {}, {}
+        for h in range(Hkv):
+            ent = []
+            for t, n in ((tobj[1], ctx // 4), (tobj[2], ctx // 2), (tobj[3], ctx // 4)):
+                ent.append((None, None, t.b_theta, n, torch.randn(n, dh, generator=cpu_gen).half().to(dev),
+                            (torch.rand(n, t.G, generator=cpu_gen).to(dev) * 3,
+                             torch.randint(0, 2 ** t.b_theta, (n, t.G), generator=cpu_gen).to(dev))))
+            per_head[(0, h)] = ent
+            for t in tobj[1:]:
+                c = torch.randn(t.G, 2 ** t.b_theta, t.g, generator=cpu_gen)
+                cbs[(0, h, t.tier_id)] = c / c.norm(dim=-1, keepdim=True)
+        pipe = SimpleNamespace(per_head_pages=per_head, codebooks=cbs)
+        cap = 64 * Hkv
+        torch.cuda.synchronize()
+        t0 = _time.perf_counter()
+        pool = sphkv_lut.LayerPool(pipe, 0, Np, 8, 64, cap, dev, tobj, idx_map, Hq, Hkv, Hq // Hkv, dh)
+        torch.cuda.synchronize()
+        build_ms = (_time.perf_counter() - t0) * 1e3
+        q = torch.randn(Hq, dh, device=dev); k = torch.randn(Hkv, dh, device=dev); v = torch.randn(Hkv, dh, device=dev)
+        sm = dh ** -0.5
+        pool.append_and_compute(q, k, v, tobj, sm)
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream(device=dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                pool.append_and_compute(q, k, v, tobj, sm)
+        torch.cuda.synchronize()
+        n_steps = min(200, (cap // Hkv - 2) * Np // 2)
+        graph_us = ev_time(g.replay, n_steps) * 1e3
+        plain_us = ev_time(lambda: pool.append_and_compute(q, k, v, tobj, sm), n_steps) * 1e3
+        pool.check_overflow()
+        if rank == 0:
+            print(json.dumps({"metric": "layerpool_step_us", "value": graph_us, "unit": "us", "n_gpus": world,
+                              "steps": n_steps, "warmup": 1, "higher_is_better": False, "data": "synthetic",
+                              "config": {"workload": f"LayerPool decode step (append with on-device page roll-over + "
+                                                     f"pool decode), 1 sequence, Hq{Hq} Hkv{Hkv} dh{dh}, ctx {ctx}, "
+                                                     f"{Np}-token pages, tiers 25/50/25; replayed from one CUDA graph"},
+                              "plain_launch_us": plain_us, "pool_pages": int(pool.num_pages_used),
+                              "bulk_construction_ms": build_ms}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -304,7 +435,7 @@ def main() -> None:
     ap.add_argument("--ema", action="store_true",
                     help="also update the page-importance EMA in the decode epilogue (per-tile statistics + "
                          "omega blend inside the merge kernel); off for the headline line")
-    ap.add_argument("--workload", default="decode", choices=["decode", "splitkv", "encode"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "splitkv", "encode", "recode", "kmeans", "pool"],
                     help="decode: the headline line (default); splitkv: one 131072-token sequence "
                          "split over the ranks; encode: prefill compression throughput")
     args = ap.parse_args()

@@ -16,9 +16,17 @@
 
 namespace sphkv {
 
-constexpr int kPoolThreads = 128;
+constexpr int kPoolThreads = 256;
 
 // ---- pool decode: per (KV head, logical page) partial (m, l, acc) for each query head ----
+// The q.centroid table depends only on (query head, tier), not on the page: a CTA builds the
+// tables of ALL tiers of its KV head once, then each of its warps walks pages on its own (no
+// CTA barrier per page): logits through the table, softmax statistics by shuffles, and one
+// pass over the page's V rows that feeds the accumulators of four query heads at a time.
+constexpr int kPoolWarps = kPoolThreads / 32;
+constexpr int kPagesPerWarp = 4;
+constexpr int kPagesPerCta = kPoolWarps * kPagesPerWarp;
+
 __global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
     const float* __restrict__ q_all, const float* __restrict__ cb_flat,
     const int* __restrict__ tier_G_arr, const int* __restrict__ tier_g_arr,
@@ -27,103 +35,215 @@ __global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
     const int* __restrict__ block_table, const int* __restrict__ bits_table,
     float* __restrict__ partial_out, int num_q_heads, int kv_groups, int num_tiers, int max_blocks,
     int page_size, int dh, int G_max, int cb_max, int g_max, float sm_scale) {
-  const int hkv = blockIdx.x, page_idx = blockIdx.y, tid = threadIdx.x;
+  const int hkv = blockIdx.x, tid = threadIdx.x;
   const int hq0 = hkv * kv_groups;
-  const int phys = block_table[hkv * max_blocks + page_idx];
-  if (phys < 0) {
-    for (int h = 0; h < kv_groups; ++h) {
-      float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
-      if (tid == 0) { po[0] = -INFINITY; po[1] = 0.f; }
-      for (int d = tid; d < dh; d += blockDim.x) po[2 + d] = 0.f;
-    }
-    return;
-  }
-  const int tier_idx = bits_table[hkv * max_blocks + page_idx];
-  const int G = tier_G_arr[tier_idx], g = tier_g_arr[tier_idx];
+  const int warp = tid >> 5, lane = tid & 31;
 
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  float* sq = reinterpret_cast<float*>(smem_raw);   // [kv_groups][dh]
-  float* lut = sq + kv_groups * dh;                  // [kv_groups][G_max][cb_max]
-  float* slog = lut + kv_groups * G_max * cb_max;    // [kv_groups][page_size]
-  float* srs = slog + kv_groups * page_size;         // [G_max]
+  float* sq = reinterpret_cast<float*>(smem_raw);                 // [kv_groups][dh]
+  float* lut = sq + kv_groups * dh;                                // [num_tiers][kv_groups][G_max][cb_max]
+  float* slog_all = lut + num_tiers * kv_groups * G_max * cb_max;  // [warps][kv_groups][page_size]
+  float* srs_all = slog_all + kPoolWarps * kv_groups * page_size;  // [warps][G_max]
+  float* slog = slog_all + warp * kv_groups * page_size;
+  float* srs = srs_all + warp * G_max;
 
   for (int i = tid; i < kv_groups * dh; i += blockDim.x) sq[i] = q_all[(int64_t)hq0 * dh + i];
-  if (tid < G_max) srs[tid] = r_scales[(int64_t)phys * G_max + tid];
   __syncthreads();
-
-  // q . centroid table for this tier; same summation order as decode_kernel.cu:186-188
-  const float* cb_t = cb_flat + ((int64_t)hkv * num_tiers + tier_idx) * G_max * cb_max * g_max;
-  for (int i = tid; i < kv_groups * G * cb_max; i += blockDim.x) {
-    const int c = i % cb_max, gg = (i / cb_max) % G, h = i / (cb_max * G);
-    const float* qg = sq + h * dh + gg * g;
-    const float* cw = cb_t + ((int64_t)gg * cb_max + c) * g_max;
-    float dot = 0.f;
-    for (int d = 0; d < g; ++d) dot += qg[d] * cw[d];
-    lut[(h * G_max + gg) * cb_max + c] = dot;
+  // q . centroid tables of every tier; same summation order as decode_kernel.cu:186-188
+  for (int ti = 0; ti < num_tiers; ++ti) {
+    const int G = tier_G_arr[ti], g = tier_g_arr[ti];
+    const float* cb_t = cb_flat + ((int64_t)hkv * num_tiers + ti) * G_max * cb_max * g_max;
+    const bool vec4 = ((g | g_max) & 3) == 0 && (reinterpret_cast<uintptr_t>(cb_flat) & 15) == 0;
+    float* lt = lut + (int64_t)ti * kv_groups * G_max * cb_max;
+    for (int i = tid; i < kv_groups * G * cb_max; i += blockDim.x) {
+      const int c = i % cb_max, gg = (i / cb_max) % G, h = i / (cb_max * G);
+      const float* qg = sq + h * dh + gg * g;
+      const float* cw = cb_t + ((int64_t)gg * cb_max + c) * g_max;
+      float dot = 0.f;
+      if (vec4) {  // same left-to-right order, 16-byte loads
+        for (int d = 0; d < g; d += 4) {
+          const float4 w4 = __ldg(reinterpret_cast<const float4*>(cw + d));
+          dot += qg[d] * w4.x;
+          dot += qg[d + 1] * w4.y;
+          dot += qg[d + 2] * w4.z;
+          dot += qg[d + 3] * w4.w;
+        }
+      } else {
+        for (int d = 0; d < g; ++d) dot += qg[d] * cw[d];
+      }
+      lt[(h * G_max + gg) * cb_max + c] = dot;
+    }
   }
   __syncthreads();
 
-  // logits: thread = token, all query heads of the KV head
-  for (int t = tid; t < page_size; t += blockDim.x) {
-    const uint8_t* th = theta_codes + ((int64_t)phys * page_size + t) * G_max;
-    const uint8_t* rc = radius_codes + ((int64_t)phys * page_size + t) * G_max;
-    for (int h = 0; h < kv_groups; ++h) {
+  const int pg0 = blockIdx.y * kPagesPerCta;
+  for (int k = 0; k < kPagesPerWarp; ++k) {
+    const int page_idx = pg0 + warp + k * kPoolWarps;  // warp-uniform
+    if (page_idx >= max_blocks) break;
+    const int phys = block_table[hkv * max_blocks + page_idx];
+    if (phys < 0) {
+      for (int h = 0; h < kv_groups; ++h) {
+        float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
+        if (lane == 0) { po[0] = -INFINITY; po[1] = 0.f; }
+        for (int d = lane; d < dh; d += 32) po[2 + d] = 0.f;
+      }
+      continue;
+    }
+    const int tier_idx = bits_table[hkv * max_blocks + page_idx];
+    const int G = tier_G_arr[tier_idx];
+    const float* lt = lut + (int64_t)tier_idx * kv_groups * G_max * cb_max;
+    __syncwarp();  // the previous page's readers of slog / srs are done
+    for (int i = lane; i < G_max; i += 32) srs[i] = r_scales[(int64_t)phys * G_max + i];
+    __syncwarp();
+    // logits: lane = (token, query head) pairs.  A byte becomes a float by planting it in the
+    // mantissa of 2^23 (exact, and keeps the conversion off the special-function pipe).
+    const bool words = (G_max & 3) == 0;
+    for (int i = lane; i < page_size * kv_groups; i += 32) {
+      const int t = i % page_size, h = i / page_size;
+      const uint8_t* th = theta_codes + ((int64_t)phys * page_size + t) * G_max;
+      const uint8_t* rc = radius_codes + ((int64_t)phys * page_size + t) * G_max;
+      const float* lh = lt + (int64_t)h * G_max * cb_max;
       float logit_sum = 0.f;
-      for (int gg = 0; gg < G; ++gg) {
-        const float r_hat = srs[gg] * (float)rc[gg] / 255.0f;
-        logit_sum += r_hat * lut[(h * G_max + gg) * cb_max + th[gg]];
+      if (words) {
+        for (int g0 = 0; g0 < G; g0 += 4) {
+          const uint32_t tw = __ldg(reinterpret_cast<const uint32_t*>(th + g0));
+          const uint32_t rw = __ldg(reinterpret_cast<const uint32_t*>(rc + g0));
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (g0 + e < G) {
+              const float rf = __uint_as_float(0x4B000000u | ((rw >> (8 * e)) & 0xFFu)) - 8388608.0f;
+              const float r_hat = srs[g0 + e] * rf / 255.0f;
+              logit_sum += r_hat * lh[(g0 + e) * cb_max + ((tw >> (8 * e)) & 0xFFu)];
+            }
+          }
+        }
+      } else {
+        for (int gg = 0; gg < G; ++gg) {
+          const float r_hat = srs[gg] * (float)rc[gg] / 255.0f;
+          logit_sum += r_hat * lh[gg * cb_max + th[gg]];
+        }
       }
       slog[h * page_size + t] = (logit_sum == 0.f) ? -1e9f : logit_sum * sm_scale;
     }
-  }
-  __syncthreads();
-
-  // per head: softmax statistics over the page and V accumulation; warp = head
-  const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < kv_groups; h += nwarps) {
-    const float* lg = slog + h * page_size;
-    float m = -INFINITY;
-    for (int t = lane; t < page_size; t += 32) m = fmaxf(m, lg[t]);
+    __syncwarp();
+    // softmax statistics per head; the logits are replaced in place by exp(logit - max)
+    for (int h = 0; h < kv_groups; ++h) {
+      float* lg = slog + h * page_size;
+      float m = -INFINITY;
+      for (int t = lane; t < page_size; t += 32) m = fmaxf(m, lg[t]);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float l = 0.f;
-    for (int t = lane; t < page_size; t += 32) l += __expf(lg[t] - m);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-    float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
-    if (lane == 0) { po[0] = m; po[1] = l; }
-    for (int d0 = 2 * lane; d0 < dh; d0 += 64) {
-      float a0 = 0.f, a1 = 0.f;
-      const __half* vp = v_pool + (int64_t)phys * page_size * dh + d0;
-      for (int t = 0; t < page_size; ++t) {
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      float l = 0.f;
+      for (int t = lane; t < page_size; t += 32) {
         const float pt = __expf(lg[t] - m);
-        const __half2 v2 = *reinterpret_cast<const __half2*>(vp + (int64_t)t * dh);
-        a0 += pt * __low2float(v2);
-        a1 += pt * __high2float(v2);
+        lg[t] = pt;
+        l += pt;
       }
-      po[2 + d0] = a0;
-      po[2 + d0 + 1] = a1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+      if (lane == 0) {
+        float* po = partial_out + ((int64_t)(hq0 + h) * max_blocks + page_idx) * (dh + 2);
+        po[0] = m;
+        po[1] = l;
+      }
+    }
+    __syncwarp();
+    // V accumulation: a lane owns 4 dimensions, one pass over the rows feeds four heads
+    for (int h0 = 0; h0 < kv_groups; h0 += 4) {
+      for (int d0 = 4 * lane; d0 < dh; d0 += 128) {
+        float acc[4][4];
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) acc[hh][0] = acc[hh][1] = acc[hh][2] = acc[hh][3] = 0.f;
+        const __half* vp = v_pool + (int64_t)phys * page_size * dh + d0;
+#pragma unroll 4
+        for (int t = 0; t < page_size; ++t) {
+          const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vp + (int64_t)t * dh));
+          const float2 va = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+          const float2 vb = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+#pragma unroll
+          for (int hh = 0; hh < 4; ++hh) {
+            if (h0 + hh < kv_groups) {
+              const float pt = slog[(h0 + hh) * page_size + t];
+              acc[hh][0] += pt * va.x;
+              acc[hh][1] += pt * va.y;
+              acc[hh][2] += pt * vb.x;
+              acc[hh][3] += pt * vb.y;
+            }
+          }
+        }
+#pragma unroll
+        for (int hh = 0; hh < 4; ++hh) {
+          if (h0 + hh < kv_groups) {
+            float* po = partial_out + ((int64_t)(hq0 + h0 + hh) * max_blocks + page_idx) * (dh + 2) + 2 + d0;
+            *reinterpret_cast<float2*>(po) = make_float2(acc[hh][0], acc[hh][1]);
+            *reinterpret_cast<float2*>(po + 2) = make_float2(acc[hh][2], acc[hh][3]);
+          }
+        }
+      }
     }
   }
 }
 
-// log-sum-exp merge of the page partials, decode_kernel.cu:221-246
-__global__ void pool_reduce_kernel(const float* __restrict__ partial_out, float* __restrict__ out,
-                                   int dh, int max_pages) {
-  const int hq = blockIdx.x;
-  for (int d = threadIdx.x; d < dh; d += blockDim.x) {
-    float m_f = -INFINITY, l_f = 0.f, a_f = 0.f;
-    for (int pg = 0; pg < max_pages; ++pg) {
-      const float* pr = partial_out + ((int64_t)hq * max_pages + pg) * (dh + 2);
-      const float m_s = pr[0], l_s = pr[1];
-      if (m_s == -INFINITY && l_s == 0.f) continue;
-      const float m_new = fmaxf(m_f, m_s);
-      const float alpha = __expf(m_f - m_new), beta = __expf(m_s - m_new);
-      a_f = alpha * a_f + beta * pr[2 + d];
-      l_f = alpha * l_f + beta * l_s;
-      m_f = m_new;
+// log-sum-exp merge of the page partials (decode_kernel.cu:221-246).  The reference folds the
+// pages into a running (max, sum, acc) one after the other; here the maximum over the pages is
+// found first and every page is weighted by exp(m_page - max) directly, which gives the same
+// result without a serial chain of rescales: one CTA per query head, pages in chunks whose
+// weights are shared through shared memory, threads over the head dimension.
+constexpr int kReduceThreads = 1024;  // 32 dimension lanes x 32 page lanes
+constexpr int kReduceChunk = 1024;
+
+// grid (query heads, dh / 32): a CTA owns 32 output dimensions of one head
+__global__ void __launch_bounds__(kReduceThreads) pool_reduce_kernel(const float* __restrict__ partial_out,
+                                                                     float* __restrict__ out, int dh,
+                                                                     int max_pages) {
+  const int hq = blockIdx.x, tid = threadIdx.x, lane = tid & 31, pl = tid >> 5;  // lane = dimension lane
+  const int d = blockIdx.y * 32 + lane;
+  __shared__ float s_w[kReduceChunk];
+  __shared__ float s_red[32];
+  __shared__ float s_acc[32][33];
+  __shared__ float s_l[32];
+  const float* base = partial_out + (int64_t)hq * max_pages * (dh + 2);
+  const int64_t row = dh + 2;
+  float M = -INFINITY;
+  for (int pg = tid; pg < max_pages; pg += kReduceThreads) {
+    const float m_s = base[pg * row], l_s = base[pg * row + 1];
+    if (!(m_s == -INFINITY && l_s == 0.f)) M = fmaxf(M, m_s);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if (lane == 0) s_red[pl] = M;
+  __syncthreads();
+  M = s_red[0];
+  for (int i = 1; i < 32; ++i) M = fmaxf(M, s_red[i]);
+  float l_f = 0.f, a_f = 0.f;
+  for (int p0 = 0; p0 < max_pages; p0 += kReduceChunk) {
+    const int np = min(kReduceChunk, max_pages - p0);
+    __syncthreads();
+    for (int i = tid; i < np; i += kReduceThreads) {
+      const float m_s = base[(p0 + i) * row], l_s = base[(p0 + i) * row + 1];
+      s_w[i] = (m_s == -INFINITY && l_s == 0.f) ? 0.f : __expf(m_s - M);
     }
-    out[(int64_t)hq * dh + d] = a_f / (l_f + 1e-8f);
+    __syncthreads();
+    // every page row was written by pool_page_kernel (zeros for holes): zero weights need no branch
+#pragma unroll 4
+    for (int i = pl; i < np; i += 32) {
+      const float w = s_w[i];
+      const float* pr = base + (p0 + i) * row;
+      l_f += w * pr[1];
+      if (d < dh) a_f += w * pr[2 + d];
+    }
+  }
+  // fold the 32 page lanes in a fixed order
+  s_acc[pl][lane] = a_f;
+  if (lane == 0) s_l[pl] = l_f;
+  __syncthreads();
+  if (pl == 0 && d < dh) {
+    float l_t = 0.f, a_t = 0.f;
+    for (int k = 0; k < 32; ++k) {
+      l_t += s_l[k];
+      a_t += s_acc[k][lane];
+    }
+    out[(int64_t)hq * dh + d] = a_t / (l_t + 1e-8f);
   }
 }
 
@@ -263,11 +383,14 @@ extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const
                     num_q_heads == num_kv_heads * kv_groups,
                 SPHKV_E_ARG, "pool_decode: Hq=%d Hkv=%d groups=%d", num_q_heads, num_kv_heads,
                 kv_groups);
-  SPHKV_REQUIRE(max_blocks > 0 && page_size > 0 && dh > 0 && (dh & 1) == 0 && G_max > 0 &&
+  SPHKV_REQUIRE(max_blocks > 0 && page_size > 0 && dh > 0 && dh <= 512 && (dh & 3) == 0 && G_max > 0 &&
                     cb_max > 0 && g_max > 0 && num_tiers > 0,
                 SPHKV_E_ARG, "pool_decode: bad size");
-  const size_t smem = ((size_t)kv_groups * dh + (size_t)kv_groups * G_max * cb_max +
-                       (size_t)kv_groups * page_size + G_max) * sizeof(float);
+  SPHKV_REQUIRE((reinterpret_cast<uintptr_t>(v_pool) & 7) == 0 && (reinterpret_cast<uintptr_t>(partial_scratch) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(theta_codes) & 3) == 0 && (reinterpret_cast<uintptr_t>(radius_codes) & 3) == 0,
+                SPHKV_E_ALIGN, "pool_decode: v_pool / partial_scratch need 8 B, code arrays 4 B alignment");
+  const size_t smem = ((size_t)kv_groups * dh + (size_t)num_tiers * kv_groups * G_max * cb_max +
+                       (size_t)kPoolWarps * ((size_t)kv_groups * page_size + G_max)) * sizeof(float);
   SPHKV_REQUIRE(smem <= 200 * 1024, SPHKV_E_LIMIT, "pool_decode: needs %zu B shared memory", smem);
   static size_t configured = 48 * 1024;
   if (smem > configured) {
@@ -280,12 +403,12 @@ extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const
     configured = smem;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  pool_page_kernel<<<dim3(num_kv_heads, max_blocks), kPoolThreads, smem, st>>>(
+  pool_page_kernel<<<dim3(num_kv_heads, (max_blocks + kPagesPerCta - 1) / kPagesPerCta), kPoolThreads, smem, st>>>(
       q_all, cb_flat, tier_G, tier_g, theta_codes, radius_codes, r_scales,
       reinterpret_cast<const __half*>(v_pool), block_table, bits_table, partial_scratch,
       num_q_heads, kv_groups, num_tiers, max_blocks, page_size, dh, G_max, cb_max, g_max, sm_scale);
   if (int rc = check_launch("pool_page_kernel")) return rc;
-  pool_reduce_kernel<<<num_q_heads, 128, 0, st>>>(partial_scratch, out, dh, max_blocks);
+  pool_reduce_kernel<<<dim3(num_q_heads, (dh + 31) / 32), kReduceThreads, 0, st>>>(partial_scratch, out, dh, max_blocks);
   return check_launch("pool_reduce_kernel");
 }
 
