@@ -7,6 +7,14 @@
 
 #include "sphkv.h"
 
+// unroll factor of the centroid loops of the similarity searches (independent fma chains in flight)
+#ifndef SPHKV_SEARCH_UNROLL
+#define SPHKV_SEARCH_UNROLL 2
+#endif
+#define SPHKV_PRAGMA_(x) _Pragma(#x)
+#define SPHKV_PRAGMA(x) SPHKV_PRAGMA_(x)
+#define SPHKV_UNROLL_SEARCH SPHKV_PRAGMA(unroll SPHKV_SEARCH_UNROLL)
+
 namespace sphkv {
 
 constexpr float kLog2e = 1.4426950408889634f;

@@ -169,7 +169,9 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
         for (int h = 0; h < 4; ++h) nsq[h] = __fmaf_rn(k[h][d], k[h][d], nsq[h]);
       float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       int code[4] = {0, 0, 0, 0};
-      for (int c = 0; c < C; ++c) {
+      SPHKV_UNROLL_SEARCH
+      SPHKV_UNROLL_SEARCH
+  for (int c = 0; c < C; ++c) {
         const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
         float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -413,6 +415,7 @@ __device__ __forceinline__ void search_slice(const float (&k)[4][32], const floa
   float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
   for (int h = 0; h < 4; ++h) code[h] = 0;
+  SPHKV_UNROLL_SEARCH
   for (int c = 0; c < C; ++c) {
     const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
     float sacc[4] = {0.f, 0.f, 0.f, 0.f};

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(kKmThreads, 2) kmeans_assign_kernel(
     int code[kPts];
 #pragma unroll
     for (int h = 0; h < kPts; ++h) { best[h] = -INFINITY; code[h] = 0; }
+    SPHKV_UNROLL_SEARCH
     for (int c = 0; c < K; ++c) {
       const float4* row = reinterpret_cast<const float4*>(c_s + c * D);
       float acc[kPts];
