@@ -344,47 +344,67 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
       if ((int)threadIdx.x < (bytes & 3)) dst[words * 4 + threadIdx.x] = im[words * 4 + threadIdx.x];
     }
 
-    // ---- dense V pages (16-bit), empty slots zero-filled: 8 elements per thread-step --------
+    // ---- dense V pages (16-bit), empty slots zero-filled ----------------------------------------
+    // One item = 8 elements (a 16-byte output chunk) of one token slot of the bundle.  A thread
+    // takes four items per round: all row lookups first, then all loads, then all stores, so four
+    // independent load chains are in flight instead of one.
     if (p.v_src != nullptr && p.v_pool != nullptr) {
-      const int per_row = dh >> 3;  // 16-byte output chunks per row
-      for (int q = 0; q < ppb; ++q) {
-        const int page = page_s[q];
-        if (page < 0) continue;
-        for (int i = threadIdx.x; i < N * per_row; i += blockDim.x) {
-          const int t = i / per_row, d = (i - t * per_row) * 8;
-          const int64_t row = p.src_index[(int64_t)page * N + t];
-          uint4 o = make_uint4(0u, 0u, 0u, 0u);
-          if (row >= 0) {
-            const int64_t off = row * p.v_row_stride + (int64_t)head * p.v_head_stride + d;
-            if (p.v_src_dtype == p.v_pool_dtype &&
-                (((uintptr_t)p.v_src + off * 2) & 15) == 0) {
-              o = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.v_src) + off));
-            } else {
-              float v[8];
-              if (p.v_src_dtype == SPHKV_F32 && (((uintptr_t)p.v_src + off * 4) & 15) == 0) {
-                const float4 a0 = ldg_stream_f4(reinterpret_cast<const float*>(p.v_src) + off);
-                const float4 a1 = ldg_stream_f4(reinterpret_cast<const float*>(p.v_src) + off + 4);
-                v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
-                v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
-              } else {
+      constexpr int kInFlight = 4;
+      const int pr_shift = 31 - __clz(dh >> 3);  // 16-byte chunks per row (dh / 8, a power of two)
+      const int items = TB << pr_shift;
+      const bool same = p.v_src_dtype == p.v_pool_dtype;
+      for (int i0 = threadIdx.x; i0 < items; i0 += kEncThreads * kInFlight) {
+        int64_t off[kInFlight], dst[kInFlight];
+        bool live[kInFlight];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = load_as_float(p.v_src, p.v_src_dtype, off + e);
-              }
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                if (p.v_pool_dtype == SPHKV_F16) {
-                  w[e] = pack_f16x2(v[2 * e], v[2 * e + 1]);
-                } else {
-                  __nv_bfloat162 hb2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                  w[e] = *reinterpret_cast<uint32_t*>(&hb2);
-                }
-              }
-              o = make_uint4(w[0], w[1], w[2], w[3]);
-            }
+        for (int u = 0; u < kInFlight; ++u) {
+          const int i = i0 + u * kEncThreads;
+          const int ts = i >> pr_shift, d = (i & ((1 << pr_shift) - 1)) * 8;
+          const int page = i < items ? page_s[ts >> n_shift] : -1;
+          const int tin = ts & (N - 1);
+          dst[u] = -1;
+          off[u] = -1;
+          if (page >= 0) {
+            dst[u] = (((int64_t)page * N + tin) * dh + d) >> 3;
+            const int64_t row = p.src_index[(int64_t)page * N + tin];
+            if (row >= 0) off[u] = row * p.v_row_stride + (int64_t)head * p.v_head_stride + d;
           }
-          reinterpret_cast<uint4*>(p.v_pool)[(((int64_t)page * N + t) * dh + d) >> 3] = o;
+          live[u] = off[u] >= 0;
         }
+        uint4 o[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u) {
+          o[u] = make_uint4(0u, 0u, 0u, 0u);
+          if (!live[u]) continue;
+          if (same && (((uintptr_t)p.v_src + off[u] * 2) & 15) == 0) {
+            o[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.v_src) + off[u]));
+          } else {
+            float v[8];
+            if (p.v_src_dtype == SPHKV_F32 && (((uintptr_t)p.v_src + off[u] * 4) & 15) == 0) {
+              const float4 a0 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off[u]));
+              const float4 a1 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off[u] + 4));
+              v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
+              v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) v[e] = load_as_float(p.v_src, p.v_src_dtype, off[u] + e);
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (p.v_pool_dtype == SPHKV_F16) {
+                w[e] = pack_f16x2(v[2 * e], v[2 * e + 1]);
+              } else {
+                __nv_bfloat162 hb2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&hb2);
+              }
+            }
+            o[u] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+          if (dst[u] >= 0) reinterpret_cast<uint4*>(p.v_pool)[dst[u]] = o[u];
       }
     }
   }
