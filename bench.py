@@ -63,6 +63,8 @@ class ClockSampler(threading.Thread):
         self.index, self.rows, self._stop_evt = index, [], threading.Event()
 
     def run(self):
+        if self._run_nvml():
+            return
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
@@ -75,6 +77,37 @@ class ClockSampler(threading.Thread):
             except Exception:
                 pass
             self._stop_evt.wait(0.1)
+
+    def _run_nvml(self) -> bool:
+        """Read-only NVML polling every 20 ms (a nvidia-smi process per sample takes > 100 ms, too
+        coarse for a sub-second timed region).  Returns False if NVML is unusable."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in vis.split(",") if v.strip().isdigit()]
+            phys = int(ids[self.index]) if self.index < len(ids) else self.index
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            bits = [("hw_slowdown", pynvml.nvmlClocksEventReasonHwSlowdown),
+                    ("hw_thermal_slowdown", pynvml.nvmlClocksEventReasonHwThermalSlowdown),
+                    ("sw_thermal_slowdown", pynvml.nvmlClocksEventReasonSwThermalSlowdown),
+                    ("sw_power_cap", pynvml.nvmlClocksEventReasonSwPowerCap)]
+            get_reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            get_reasons(h)
+        except Exception:
+            return False
+        while not self._stop_evt.is_set():
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                r = get_reasons(h)
+                self.rows.append([str(sm), str(mx)] + ["Active" if r & b else "Not Active" for _, b in bits])
+            except Exception:
+                pass
+            self._stop_evt.wait(0.02)
+        return True
 
     def stop(self) -> dict:
         self._stop_evt.set()

@@ -11,6 +11,9 @@
 #ifndef SPHKV_SEARCH_UNROLL
 #define SPHKV_SEARCH_UNROLL 2
 #endif
+#ifndef SPHKV_CODE_TOKENS
+#define SPHKV_CODE_TOKENS 2
+#endif
 #define SPHKV_PRAGMA_(x) _Pragma(#x)
 #define SPHKV_PRAGMA(x) SPHKV_PRAGMA_(x)
 #define SPHKV_UNROLL_SEARCH SPHKV_PRAGMA(unroll SPHKV_SEARCH_UNROLL)

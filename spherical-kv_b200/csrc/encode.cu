@@ -429,21 +429,26 @@ struct CodesArgs {
   sphkv_tiers tiers;
 };
 
+// tokens per thread of the code-cache kernel: 2 keeps it at two CTAs per SM (<= 128 registers)
+constexpr int kCodeTok = SPHKV_CODE_TOKENS;
+
 template <int OFF, int GS>
-__device__ __forceinline__ void search_slice(const float (&k)[4][32], const float* __restrict__ cbg, int C,
-                                             int (&code)[4]) {
-  float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+__device__ __forceinline__ void search_slice(const float (&k)[kCodeTok][32], const float* __restrict__ cbg, int C,
+                                             int (&code)[kCodeTok]) {
+  float best[kCodeTok];
 #pragma unroll
-  for (int h = 0; h < 4; ++h) code[h] = 0;
+  for (int h = 0; h < kCodeTok; ++h) { best[h] = -INFINITY; code[h] = 0; }
   SPHKV_UNROLL_SEARCH
   for (int c = 0; c < C; ++c) {
     const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
-    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+    float sacc[kCodeTok];
+#pragma unroll
+    for (int h = 0; h < kCodeTok; ++h) sacc[h] = 0.f;
 #pragma unroll
     for (int i = 0; i < GS / 4; ++i) {
       const float4 v = row[i];
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
+      for (int h = 0; h < kCodeTok; ++h) {
         sacc[h] = __fmaf_rn(k[h][OFF + 4 * i], v.x, sacc[h]);
         sacc[h] = __fmaf_rn(k[h][OFF + 4 * i + 1], v.y, sacc[h]);
         sacc[h] = __fmaf_rn(k[h][OFF + 4 * i + 2], v.z, sacc[h]);
@@ -451,19 +456,19 @@ __device__ __forceinline__ void search_slice(const float (&k)[4][32], const floa
       }
     }
 #pragma unroll
-    for (int h = 0; h < 4; ++h)
+    for (int h = 0; h < kCodeTok; ++h)
       if (sacc[h] > best[h]) { best[h] = sacc[h]; code[h] = c; }
   }
 }
 
-__global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesArgs a) {
+__global__ void __launch_bounds__(kEncThreads, kCodeTok <= 2 ? 2 : 1) encode_codes_kernel(const CodesArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   float* cb_s = reinterpret_cast<float*>(smem);
   const int head = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G32 = a.dh >> 5;                  // 32-dim groups per head: 2 or 4
   const int grp = warp % G32, set = warp / G32;
-  const int sets = (kEncThreads / 32) / G32;  // token sets of 128 per CTA
+  const int sets = (kEncThreads / 32) / G32;  // token sets of 32 * kCodeTok per CTA
   // stage every slot's codebook of this head: [G_s][C_s][g_s] packed
   for (int s = 0; s < a.tiers.n_slots; ++s) {
     const int gs = a.tiers.g[s], bits = a.tiers.bits[s], G = a.dh / gs, q4n = gs >> 2;
@@ -478,11 +483,11 @@ __global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesAr
   }
   __syncthreads();
 
-  const int64_t row0 = ((int64_t)blockIdx.x * sets + set) * 128;
-  float k[4][32];
-  bool have[4];
+  const int64_t row0 = ((int64_t)blockIdx.x * sets + set) * (32 * kCodeTok);
+  float k[kCodeTok][32];
+  bool have[kCodeTok];
 #pragma unroll
-  for (int h = 0; h < 4; ++h) {
+  for (int h = 0; h < kCodeTok; ++h) {
     const int64_t row = row0 + lane + 32 * h;
     have[h] = row < a.rows;
     if (have[h]) {
@@ -492,25 +497,27 @@ __global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesAr
       for (int i = 0; i < 32; ++i) k[h][i] = 0.f;
     }
   }
-  float na[4] = {0.f, 0.f, 0.f, 0.f}, nb[4] = {0.f, 0.f, 0.f, 0.f}, nab[4];
+  float na[kCodeTok], nb[kCodeTok], nab[kCodeTok];
+#pragma unroll
+  for (int h = 0; h < kCodeTok; ++h) na[h] = nb[h] = 0.f;
 #pragma unroll
   for (int d = 0; d < 16; ++d)
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
+    for (int h = 0; h < kCodeTok; ++h) {
       na[h] = __fmaf_rn(k[h][d], k[h][d], na[h]);
       nb[h] = __fmaf_rn(k[h][16 + d], k[h][16 + d], nb[h]);
     }
 #pragma unroll
-  for (int h = 0; h < 4; ++h) nab[h] = na[h];
+  for (int h = 0; h < kCodeTok; ++h) nab[h] = na[h];
 #pragma unroll
   for (int d = 16; d < 32; ++d)
 #pragma unroll
-    for (int h = 0; h < 4; ++h) nab[h] = __fmaf_rn(k[h][d], k[h][d], nab[h]);
+    for (int h = 0; h < kCodeTok; ++h) nab[h] = __fmaf_rn(k[h][d], k[h][d], nab[h]);
 
   for (int s = 0; s < a.tiers.n_slots; ++s) {
     if (a.r_out[s] == nullptr) continue;
     const int bits = a.tiers.bits[s], C = 1 << bits;
-    int code[4];
+    int code[kCodeTok];
     if (a.tiers.g[s] == 16) {
       const int G = a.dh >> 4;
 #pragma unroll
@@ -521,7 +528,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesAr
         else
           search_slice<16, 16>(k, cb_s + a.cb_off[s] + (gam << bits) * 16, C, code);
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
+        for (int h = 0; h < kCodeTok; ++h) {
           if (!have[h]) continue;
           const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G + gam;
           a.r_out[s][o] = __fsqrt_rn(half == 0 ? na[h] : nb[h]);
@@ -531,7 +538,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_codes_kernel(const CodesAr
     } else {
       search_slice<0, 32>(k, cb_s + a.cb_off[s] + (grp << bits) * 32, C, code);
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
+      for (int h = 0; h < kCodeTok; ++h) {
         if (!have[h]) continue;
         const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G32 + grp;
         a.r_out[s][o] = __fsqrt_rn(nab[h]);
@@ -735,8 +742,8 @@ extern "C" int sphkv_encode_codes(const void* k_src, int32_t k_dtype, int64_t k_
     }
     configured = smem_bytes;
   }
-  const int sets = (kEncThreads / 32) / (dh >> 5);
-  const dim3 grid((unsigned)((rows + sets * 128 - 1) / (sets * 128)), (unsigned)Hkv);
+  const int per_cta = (kEncThreads / 32) / (dh >> 5) * 32 * kCodeTok;  // rows per CTA
+  const dim3 grid((unsigned)((rows + per_cta - 1) / per_cta), (unsigned)Hkv);
   encode_codes_kernel<<<grid, kEncThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("encode_codes_kernel");
 }
