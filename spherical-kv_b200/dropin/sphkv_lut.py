@@ -55,6 +55,38 @@ def make_tier_idx_map(tiers) -> Dict[int, int]:
     return out
 
 
+def plan_pool_pages(shapes, page_size: int):
+    """Page descriptors and per-head block lists of a pool, in the page order of
+    LayerPool.__init__ (sphkv_lut.py:37-68: heads, then segments, then pages of a segment).
+
+    shapes[h] = [(tier index, G of the tier, n_tokens), ...].  Returns (desc i32 [n_pages, 4] =
+    {first source row, rows in the page, G, physical page id}, per-head arrays of page ids, per-head
+    arrays of tier indices).  Array arithmetic per segment; nothing iterates over pages."""
+    desc_parts, head_pids, head_tidx = [], [], []
+    row0, pid0 = 0, 0
+    for segs in shapes:
+        pids_h, tidx_h = [], []
+        for t_idx, G_t, n_tokens in segs:
+            n_pages = (n_tokens + page_size - 1) // page_size
+            if n_pages == 0:
+                continue
+            first = np.arange(n_pages, dtype=np.int64) * page_size
+            d = np.empty((n_pages, 4), dtype=np.int32)
+            d[:, 0] = row0 + first
+            d[:, 1] = np.minimum(page_size, n_tokens - first)
+            d[:, 2] = G_t
+            d[:, 3] = pid0 + np.arange(n_pages)
+            desc_parts.append(d)
+            pids_h.append(d[:, 3].copy())
+            tidx_h.append(np.full(n_pages, t_idx, dtype=np.int32))
+            row0 += n_tokens
+            pid0 += n_pages
+        head_pids.append(np.concatenate(pids_h) if pids_h else np.zeros(0, np.int32))
+        head_tidx.append(np.concatenate(tidx_h) if tidx_h else np.zeros(0, np.int32))
+    desc = np.concatenate(desc_parts) if desc_parts else np.zeros((0, 4), np.int32)
+    return desc, head_pids, head_tidx
+
+
 class LayerPool:
     """LayerPool of sphkv_lut.py:18-148 built in bulk on the device."""
 
@@ -74,20 +106,18 @@ class LayerPool:
         self.g_max = max(t.g for t in active)
 
         # ---- page descriptors: one pass over (head, segment), never over pages -------------
-        r_parts, th_parts, v_parts, desc_parts = [], [], [], []
-        head_pids, head_tidx = [], []
-        row0, pid0 = 0, 0
+        r_parts, th_parts, v_parts = [], [], []
+        shapes = []
         for h in range(num_kv):
-            pids_h, tidx_h = [], []
+            segs = []
             for seg in pipeline.per_head_pages.get((layer_idx, h), []):
                 _pt, _ptt, b_theta, n_tokens, V_tier, K_tier = seg[:6]
                 r_full, theta_full = K_tier
                 tier_obj = next(t for t in active if t.b_theta == b_theta)
-                t_idx = tier_idx_map[tier_obj.tier_id]
-                G_t = tier_obj.G
-                n_pages = (n_tokens + page_size - 1) // page_size
-                if n_pages == 0:
+                segs.append((tier_idx_map[tier_obj.tier_id], tier_obj.G, n_tokens))
+                if n_tokens == 0:
                     continue
+                G_t = tier_obj.G
                 r_pad = torch.zeros(n_tokens, G_max, dtype=torch.float32, device=device)
                 r_pad[:, :G_t] = r_full[:n_tokens].detach().to(device, torch.float32)
                 t_pad = torch.zeros(n_tokens, G_max, dtype=torch.uint8, device=device)
@@ -96,19 +126,9 @@ class LayerPool:
                 r_parts.append(r_pad)
                 th_parts.append(t_pad)
                 v_parts.append(v_seg if v_seg.dtype in _DT else v_seg.float())
-                first = np.arange(n_pages, dtype=np.int64) * page_size
-                d = np.empty((n_pages, 4), dtype=np.int32)
-                d[:, 0] = row0 + first
-                d[:, 1] = np.minimum(page_size, n_tokens - first)
-                d[:, 2] = G_t
-                d[:, 3] = pid0 + np.arange(n_pages)
-                desc_parts.append(d)
-                pids_h.append(d[:, 3].copy())
-                tidx_h.append(np.full(n_pages, t_idx, dtype=np.int32))
-                row0 += n_tokens
-                pid0 += n_pages
-            head_pids.append(np.concatenate(pids_h) if pids_h else np.zeros(0, np.int32))
-            head_tidx.append(np.concatenate(tidx_h) if tidx_h else np.zeros(0, np.int32))
+            shapes.append(segs)
+        desc_np, head_pids, head_tidx = plan_pool_pages(shapes, page_size)
+        pid0 = desc_np.shape[0]
 
         n_used = pid0
         n_total = n_used + decode_capacity
@@ -127,7 +147,7 @@ class LayerPool:
             if len({v.dtype for v in v_parts}) > 1:
                 v_parts = [v.float() for v in v_parts]
             r_all, th_all, v_all = torch.cat(r_parts), torch.cat(th_parts), torch.cat(v_parts).contiguous()
-            desc = torch.from_numpy(np.concatenate(desc_parts)).to(device)
+            desc = torch.from_numpy(desc_np).to(device)
             _lib.check(_L.sphkv_pool_build_pages(
                 r_all.data_ptr(), th_all.data_ptr(), v_all.data_ptr(), _DT[v_all.dtype], G_max, dh,
                 desc.data_ptr(), n_used, self.theta_codes.data_ptr(), self.radius_codes.data_ptr(),

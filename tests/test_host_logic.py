@@ -125,3 +125,38 @@ def test_tier_set_codebook_packing():
     c = tiers.to_c()
     assert (c.n_slots, c.G_max, c.C_max, c.g_max) == (3, 8, 64, 32)
     assert list(c.g)[:3] == [16, 16, 32] and list(c.bits)[:3] == [6, 4, 3]
+
+
+def test_pool_page_planner_matches_reference_tables():
+    """the drop-in LayerPool's page plan (array arithmetic, no per-page loop) gives the
+    reference LayerPool's block table, bits table and page count (golden fixture), and its
+    descriptors cover every source row exactly once in page order"""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "spherical-kv_b200", "dropin"))
+    import sphkv_lut
+    z = np.load(os.path.join(ROOT, "tests", "golden", "layer_pool.npz"))
+    num_kv, grp, dh, page, cap, steps, G_max, cb_max = (int(x) for x in z["shape"])
+    idx_map = {int(k): int(v) for k, v in z["tier_idx"]}
+    G_of = {t.tier_id: dh // t.g for t in pkg.REFERENCE_TIERS}
+    shapes = []
+    for h in range(num_kv):
+        segs = []
+        for si in range(int(z[f"h{h}_nseg"])):
+            tid = int(z[f"h{h}_s{si}_tier"])
+            segs.append((idx_map[tid], G_of[tid], z[f"h{h}_s{si}_r"].shape[0]))
+        shapes.append(segs)
+    shapes[0].insert(1, (0, 8, 0))  # an empty segment contributes nothing
+    desc, head_pids, head_tidx = sphkv_lut.plan_pool_pages(shapes, page)
+    assert desc.shape[0] == int(z["n_used0"])
+    bt, bi = z["block_table0"], z["bits_table0"]
+    for h in range(num_kv):
+        n = len(head_pids[h])
+        np.testing.assert_array_equal(bt[h, :n], head_pids[h])
+        np.testing.assert_array_equal(bi[h, :n], head_tidx[h])
+        assert (bt[h, n:] == -1).all() and n * page == int(z["ctx_lens0"][h])
+    np.testing.assert_array_equal(desc[:, 3], np.arange(desc.shape[0]))
+    assert (desc[:, 1] >= 1).all() and (desc[:, 1] <= page).all()
+    total = sum(n for segs in shapes for _, _, n in segs)
+    covered = np.concatenate([np.arange(r0, r0 + n) for r0, n in desc[:, :2]])
+    np.testing.assert_array_equal(covered, np.arange(total))
+    assert sphkv_lut.make_tier_idx_map([type("T", (), {"tier_id": i})() for i in (0, 1, 2, 3)]) == {1: 0, 2: 1, 3: 2}
