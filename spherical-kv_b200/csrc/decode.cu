@@ -37,7 +37,7 @@ namespace sphkv {
 constexpr int kWarps = SPHKV_WARPS;
 constexpr int kCbPitch = SPHKV_CB_DUP ? 128 : 64;  // bytes per 16-dim codebook sub-row slot
 #ifndef SPHKV_VSTAGES
-#define SPHKV_VSTAGES 3
+#define SPHKV_VSTAGES 2
 #endif
 constexpr int kVStages = SPHKV_VSTAGES;  // V tiles in flight per warp: tile k + kVStages - 1 is
                                          // copied while tile k is consumed, so >= 2
@@ -77,7 +77,8 @@ struct DecodeArgs {
 
 // shared-memory carve-up, shared by host and device
 __host__ __device__ constexpr int smem_v_bytes(int dh) { return kWarps * kVStages * 16 * dh * 2; }
-__host__ __device__ constexpr int smem_q_bytes(int dh) { return 2 * (dh / 16) * 32 * 8; }
+// query fragments: hi and lo copies, or one copy when both halves share the 8 MMA columns (packed)
+__host__ __device__ constexpr int smem_q_bytes(int dh, bool pack) { return (pack ? 1 : 2) * (dh / 16) * 32 * 8; }
 __host__ __device__ constexpr int smem_priv_bytes(int dh) {
   return 16 * (dh / 16) * 8 + 512 + kMetaRing * 16;
 }
@@ -300,8 +301,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   uint8_t* v_ring = smem + warp * V_WARP;
   uint8_t* cb_smem = smem + smem_v_bytes(DH);
   const uint8_t* cb_lane = cb_smem + j * 16 + (SPHKV_CB_DUP ? (r & 1) * 64 : 0);  // this lane's chunk of its copy
-  uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [2][KS][32]
-  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) + warp * smem_priv_bytes(DH);
+  uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [PACK ? 1 : 2][KS][32]
+  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH, PACK) + warp * smem_priv_bytes(DH);
   uint2* unp = reinterpret_cast<uint2*>(warp_priv);                       // [16][KS]
   uint16_t* pbuf = reinterpret_cast<uint16_t*>(warp_priv + 16 * KS * 8);  // [2][8][16]
   TileMeta* meta = reinterpret_cast<TileMeta*>(warp_priv + 16 * KS * 8 + 512);
@@ -310,7 +311,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   //      merge kernel), or read from the plan kernel's output when there are many units ----
   const int32_t* pfx = a.pfx;
   if (a.plan_in_kernel) {
-    int32_t* pfx_s = reinterpret_cast<int32_t*>(cb_smem + a.cb_smem_bytes + smem_q_bytes(DH) +
+    int32_t* pfx_s = reinterpret_cast<int32_t*>(cb_smem + a.cb_smem_bytes + smem_q_bytes(DH, PACK) +
                                                 kWarps * smem_priv_bytes(DH));
     if (warp == 0) {
       int carry = 0;
@@ -498,7 +499,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         const float4* rp = reinterpret_cast<const float4*>(p.rope_table + (int64_t)pos * DH) + j * 2;
 #pragma unroll
         for (int s = 0; s < HS; ++s) {
-          // through L1 on purpose: a lane's cos and sin vectors share a 32-byte sector
+          // through L1 on purpose: a lane's cos and sin vectors share a 32-byte sector (and one
+          // 256-bit load for both measured slower than the two 128-bit ones)
           cs[tk][s][0] = __ldg(rp + s * 8);
           cs[tk][s][1] = __ldg(rp + s * 8 + 1);
         }
@@ -1053,6 +1055,10 @@ static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st)
       set_error("cudaFuncSetAttribute(decode, %d B): %s", smem_bytes, cudaGetErrorString(e));
       return (int)e;
     }
+    // Ask for the smallest shared-memory carve-out that holds this CTA (plus the 1 KB the system
+    // reserves): what is left of the 256 KB array is L1, which serves the cos/sin table rows.
+    const int pct = (int)(((int64_t)smem_bytes + 1024) * 100 / (228 * 1024)) + 1;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, pct > 100 ? 100 : pct);
     configured_for = smem_bytes;
   }
   kern<<<a.n_ctas, kWarps * 32, smem_bytes, st>>>(a);
@@ -1152,7 +1158,7 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
                                     align_up((int64_t)(a.n_units + 1) * 4, 256));
   a.cb_smem_bytes = smem_cb_layout(p.tiers, p.dh, a.cb_smem_off);
   a.plan_in_kernel = a.n_units <= kMaxUnitsInKernelPlan ? 1 : 0;
-  const int smem_bytes = smem_v_bytes(p.dh) + a.cb_smem_bytes + smem_q_bytes(p.dh) +
+  const int smem_bytes = smem_v_bytes(p.dh) + a.cb_smem_bytes + smem_q_bytes(p.dh, a.grp <= 4) +
                          kWarps * smem_priv_bytes(p.dh) +
                          (a.plan_in_kernel ? (a.n_units + 1) * 4 : 0);
   SPHKV_REQUIRE(smem_bytes <= 227 * 1024, SPHKV_E_LIMIT,
