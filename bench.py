@@ -441,6 +441,30 @@ def run_side_workload(args) -> None:
         graph_us = ev_time(g.replay, n_steps) * 1e3
         plain_us = ev_time(lambda: pool.append_and_compute(q, k, v, tobj, sm), n_steps) * 1e3
         pool.check_overflow()
+        # same-box GPU comparison: the reference's own CUDA kernels (compiled from the reference tree
+        # into oracle/_ref/ by oracle/build_ref.py) on the same data at 128-token pages, the only
+        # page size their launch geometry supports; skipped when the module is not there
+        ref_cmp = None
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle"))
+        import build_ref
+        ref_mod = build_ref.load_module()
+        if ref_mod is not None:
+            pool128 = sphkv_lut.LayerPool(pipe, 0, 128, 8, 64, 8 * Hkv, dev, tobj, idx_map, Hq, Hkv, Hq // Hkv, dh)
+            out_r = torch.zeros(Hq, dh, device=dev)
+            part_r = torch.zeros(Hq, pool128.max_blocks, dh + 2, device=dev)
+            dargs = (q, pool128.cb_flat, pool128.tier_G_gpu, pool128.tier_g_gpu, pool128.theta_codes,
+                     pool128.radius_codes, pool128.r_scales, pool128.v_pool, pool128.block_table_gpu,
+                     pool128.bits_table_gpu, pool128.ctx_lens_gpu)
+            tail = (Hq, Hkv, Hq // Hkv, len(idx_map), pool128.max_blocks, 128, dh, 8, 64, pool128.g_max, sm, ctx)
+            import fused_decode as ours
+            ref_fn = lambda: ref_mod.forward(*dargs, out_r, part_r, *tail)  # noqa: E731
+            our_fn = lambda: ours.sphkv_decode(*dargs, pool128._out_buf, pool128._partial_scratch, *tail)  # noqa: E731
+            for _ in range(3):
+                ref_fn(); our_fn()
+            torch.cuda.synchronize()
+            diff = float((out_r - pool128._out_buf).abs().max().item())
+            ref_cmp = {"page_size": 128, "reference_cuda_decode_us": ev_time(ref_fn, 50) * 1e3,
+                       "this_library_decode_us": ev_time(our_fn, 50) * 1e3, "max_abs_diff": diff}
         if rank == 0:
             print(json.dumps({"metric": "layerpool_step_us", "value": graph_us, "unit": "us", "n_gpus": world,
                               "steps": n_steps, "warmup": 1, "higher_is_better": False, "data": "synthetic",
@@ -448,7 +472,8 @@ def run_side_workload(args) -> None:
                                                      f"pool decode), 1 sequence, Hq{Hq} Hkv{Hkv} dh{dh}, ctx {ctx}, "
                                                      f"{Np}-token pages, tiers 25/50/25; replayed from one CUDA graph"},
                               "plain_launch_us": plain_us, "pool_pages": int(pool.num_pages_used),
-                              "bulk_construction_ms": build_ms}), flush=True)
+                              "bulk_construction_ms": build_ms,
+                              "same_box_reference_kernel": ref_cmp}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -24,8 +24,7 @@ constexpr int kPoolThreads = 256;
 // CTA barrier per page): logits through the table, softmax statistics by shuffles, and one
 // pass over the page's V rows that feeds the accumulators of four query heads at a time.
 constexpr int kPoolWarps = kPoolThreads / 32;
-constexpr int kPagesPerWarp = 4;
-constexpr int kPagesPerCta = kPoolWarps * kPagesPerWarp;
+constexpr int kMaxPagesPerWarp = 4;  // fewer when the grid would not fill the GPU
 
 __global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
     const float* __restrict__ q_all, const float* __restrict__ cb_flat,
@@ -34,7 +33,7 @@ __global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
     const float* __restrict__ r_scales, const __half* __restrict__ v_pool,
     const int* __restrict__ block_table, const int* __restrict__ bits_table,
     float* __restrict__ partial_out, int num_q_heads, int kv_groups, int num_tiers, int max_blocks,
-    int page_size, int dh, int G_max, int cb_max, int g_max, float sm_scale) {
+    int page_size, int dh, int G_max, int cb_max, int g_max, float sm_scale, int pages_per_warp) {
   const int hkv = blockIdx.x, tid = threadIdx.x;
   const int hq0 = hkv * kv_groups;
   const int warp = tid >> 5, lane = tid & 31;
@@ -76,8 +75,8 @@ __global__ void __launch_bounds__(kPoolThreads) pool_page_kernel(
   }
   __syncthreads();
 
-  const int pg0 = blockIdx.y * kPagesPerCta;
-  for (int k = 0; k < kPagesPerWarp; ++k) {
+  const int pg0 = blockIdx.y * kPoolWarps * pages_per_warp;
+  for (int k = 0; k < pages_per_warp; ++k) {
     const int page_idx = pg0 + warp + k * kPoolWarps;  // warp-uniform
     if (page_idx >= max_blocks) break;
     const int phys = block_table[hkv * max_blocks + page_idx];
@@ -365,6 +364,12 @@ __global__ void ragged_logits_kernel(const uint8_t* __restrict__ pages,
 
 using namespace sphkv;
 
+static int sphkv_sm_count_or(int fallback) {
+  static int sms = 0;
+  if (sms <= 0) sms = sphkv_sm_count();
+  return sms > 0 ? sms : fallback;
+}
+
 extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const int32_t* tier_G,
                                  const int32_t* tier_g, const uint8_t* theta_codes,
                                  const uint8_t* radius_codes, const float* r_scales,
@@ -403,10 +408,14 @@ extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const
     configured = smem;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  pool_page_kernel<<<dim3(num_kv_heads, (max_blocks + kPagesPerCta - 1) / kPagesPerCta), kPoolThreads, smem, st>>>(
+  // pages per warp: up to kMaxPagesPerWarp (amortises the table build), fewer while the grid is small
+  int ppw = (int)(((int64_t)num_kv_heads * max_blocks) / ((int64_t)kPoolWarps * 2 * sphkv_sm_count_or(148)));
+  ppw = ppw < 1 ? 1 : (ppw > kMaxPagesPerWarp ? kMaxPagesPerWarp : ppw);
+  const int ppc = kPoolWarps * ppw;
+  pool_page_kernel<<<dim3(num_kv_heads, (max_blocks + ppc - 1) / ppc), kPoolThreads, smem, st>>>(
       q_all, cb_flat, tier_G, tier_g, theta_codes, radius_codes, r_scales,
       reinterpret_cast<const __half*>(v_pool), block_table, bits_table, partial_scratch,
-      num_q_heads, kv_groups, num_tiers, max_blocks, page_size, dh, G_max, cb_max, g_max, sm_scale);
+      num_q_heads, kv_groups, num_tiers, max_blocks, page_size, dh, G_max, cb_max, g_max, sm_scale, ppw);
   if (int rc = check_launch("pool_page_kernel")) return rc;
   pool_reduce_kernel<<<dim3(num_q_heads, (dh + 31) / 32), kReduceThreads, 0, st>>>(partial_scratch, out, dh, max_blocks);
   return check_launch("pool_reduce_kernel");
