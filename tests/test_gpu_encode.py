@@ -136,3 +136,53 @@ def test_encode_matches_reference_golden_pages():
                 assert (th_g != th_r).sum() <= max(1, n * G // 500)
                 rc_g = got[r_rel:].view(np.int8).astype(int); rc_r = ref[r_rel:].view(np.int8).astype(int)
                 assert np.abs(rc_g - rc_r).max() <= 1 and (rc_g != rc_r).mean() < 0.02
+
+
+@pytest.mark.parametrize("use_scratch", [True, False])
+def test_encode_ties_and_near_ties_pick_the_chain_argmax(use_scratch):
+    """codebooks with duplicated rows (exact ties: the lowest index must win), rows one or a few
+    ulps apart, and keys that are exact centroids, bisectors, zeros, huge and tiny vectors: the
+    pages stay byte-identical to the fp32-chain oracle (this drives the exact re-check of the
+    tensor-core search on most token-groups)"""
+    dev = torch.device("cuda:0")
+    dh, Hkv, T, N = 128, 2, 512, 16
+    specs = pkg.REFERENCE_TIERS[:2]
+    tiers = pkg.TierSet(dh, specs)
+    cbs = synth.make_codebooks(Hkv, dh, specs, seed=41)
+    g = torch.Generator().manual_seed(42)
+    for s, t in enumerate(specs):
+        cb = cbs[s]                                   # [Hkv, G, C, 16]
+        C = cb.shape[2]
+        cb[:, :, 1] = cb[:, :, 0]                     # exact duplicate of row 0
+        cb[:, :, 3] = torch.nextafter(cb[:, :, 2], torch.full_like(cb[:, :, 2], 10.0))   # +1 ulp
+        cb[:, :, 5] = cb[:, :, 4] * (1.0 + 3e-7)      # a few ulps
+        cb[:, :, C - 1] = cb[:, :, C - 2]             # duplicate at the end
+    K = torch.randn(T, Hkv, dh, generator=g)
+    G = dh // 16
+    for i in range(T):
+        mode = i % 8
+        h = i % Hkv
+        src = cbs[0][h]                               # tier-1 centroids of this head, [G, 64, 16]
+        if mode == 0:
+            K[i, h] = (src[:, i % 64] * 2.5).reshape(dh)                         # exactly a (scaled) centroid
+        elif mode == 1:
+            K[i, h] = (src[:, 0] + src[:, 2]).reshape(dh)                        # bisector of two rows
+        elif mode == 2:
+            K[i, h] = (src[:, 4] * 0.7 + src[:, 5] * 0.7).reshape(dh)            # between near-duplicates
+        elif mode == 3:
+            K[i] = 0.0                                                           # zero vector
+        elif mode == 4:
+            K[i] *= 1e4
+        elif mode == 5:
+            K[i] *= 1e-6
+        elif mode == 6:
+            K[i, h] = (src[:, 62] * -1.0).reshape(dh)                            # opposite of a row
+    assign = synth.make_tier_assign(1, Hkv, T, {1: 0.5, 2: 0.5}, seed=43, per_head=True)
+    lists = pkg.build_page_lists(assign, tiers, N, shuffle_seed=3)
+    dl = pkg.PageLists(**{k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in lists.__dict__.items()})
+    cache = pkg.encode_pages(K.to(dev), None, dl, tiers.pack_codebooks(cbs).to(dev), tiers, use_scratch=use_scratch)
+    torch.cuda.synchronize()
+    want = oracle_pages(K.reshape(1, T, Hkv, dh), assign, lists, tiers, cbs, 0)
+    got = cache.k_pages.cpu().numpy()
+    bad = np.nonzero(got != want)[0]
+    assert bad.size == 0, f"{bad.size} byte(s) differ, first at {bad[:8]}"
