@@ -90,7 +90,8 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   float* scale_s = r_s + TB * G;                                       // [8][8]
   int* count_s = reinterpret_cast<int*>(scale_s + 64);                 // [8]
   int* page_s = count_s + 8;                                           // [8]
-  uint8_t* th_s = reinterpret_cast<uint8_t*>(page_s + 8);              // [TB][G]
+  int* poff_s = page_s + 8;                                            // [8] byte offset of each page
+  uint8_t* th_s = reinterpret_cast<uint8_t*>(poff_s + 8);              // [TB][G]
   uint8_t* img = th_s + TB * G;                                        // page images, 16-aligned
   img = reinterpret_cast<uint8_t*>(((uintptr_t)img + 15) & ~(uintptr_t)15);
 
@@ -111,7 +112,11 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
           cnt += __popc(__ballot_sync(0xffffffffu, ok));
         }
       }
-      if (lane == 0) { count_s[warp] = cnt; page_s[warp] = page; }
+      if (lane == 0) {
+        count_s[warp] = cnt;
+        page_s[warp] = page;
+        poff_s[warp] = page >= 0 ? p.ptable[3 * (int64_t)page] : 0;
+      }
     }
     __syncthreads();
     int first = -1;
@@ -262,86 +267,96 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     __syncthreads();
 
     // ---- page images: header, scales, packed theta words ---------------------------------------
-    for (int q = 0; q < ppb; ++q) {
-      const int cnt = count_s[q];
-      if (cnt == 0) continue;
-      uint8_t* im = img + q * img_stride;
-      const int tbase = q * N;
-      const int hdr = 8 + 4 * G;
-      const int nvals = cnt * G;
-      const int th_bytes = (nvals * bits + 7) >> 3;
-      const int th_words = (th_bytes + 3) >> 2;
-      if (threadIdx.x < 2) {
+    // Every loop below runs over the whole bundle (all pages at once), so the CTA's threads share
+    // the work of the 128 / page_size pages evenly instead of a fraction of them looping per page.
+    const int hdr = 8 + 4 * G;
+    if ((int)threadIdx.x < 2 * ppb) {
+      const int q = threadIdx.x >> 1, cnt = count_s[q];
+      if (cnt > 0) {
         uint32_t w = 0;
-        if (threadIdx.x == 0)
+        if ((threadIdx.x & 1) == 0)
           w = (uint32_t)(p.tiers.tier_id[slot] & 0xFF) | ((uint32_t)(cnt & 0xFF) << 8) |
               ((uint32_t)(p.radius_fmt & 0xFF) << 16);
-        reinterpret_cast<uint32_t*>(im)[threadIdx.x] = w;
+        reinterpret_cast<uint32_t*>(img + q * img_stride)[threadIdx.x & 1] = w;
       }
-      if (threadIdx.x < G) reinterpret_cast<float*>(im + 8)[threadIdx.x] = scale_s[q * 8 + threadIdx.x];
-      for (int w = threadIdx.x; w < th_words; w += blockDim.x) {
+    }
+    if ((int)threadIdx.x < 8 * ppb) {
+      const int q = threadIdx.x >> 3, gq = threadIdx.x & 7;
+      if (gq < G && count_s[q] > 0)
+        reinterpret_cast<float*>(img + q * img_stride + 8)[gq] = scale_s[q * 8 + gq];
+    }
+    {
+      const int max_words = ((((N * G * bits + 7) >> 3) + 3) >> 2);
+      for (int it = threadIdx.x; it < ppb * max_words; it += blockDim.x) {
+        const int q = it / max_words, w = it - q * max_words;
+        const int nvals = count_s[q] * G;
+        const int th_words = ((((nvals * bits + 7) >> 3) + 3) >> 2);
+        if (w >= th_words) continue;
         const int bit0 = w * 32;
         int i = bit0 / bits;  // first value overlapping this word
         uint32_t acc = 0;
         for (; i < nvals && i * bits < bit0 + 32; ++i) {
-          const uint32_t v = th_s[tbase * G + i];
+          const uint32_t v = th_s[q * N * G + i];
           const int sh = i * bits - bit0;
           acc |= sh >= 0 ? (v << sh) : (v >> (-sh));
         }
-        reinterpret_cast<uint32_t*>(im + hdr)[w] = acc;
+        reinterpret_cast<uint32_t*>(img + q * img_stride + hdr)[w] = acc;
       }
     }
     __syncthreads();
     // ---- radii (may overlay the zero tail of the last theta word) ----------------------------
-    for (int q = 0; q < ppb; ++q) {
+    for (int i = threadIdx.x; i < TB * G; i += blockDim.x) {
+      const int ts = i >> g_shift, gq = i & (G - 1);
+      const int q = ts >> n_shift, tin = ts & (N - 1);
       const int cnt = count_s[q];
-      if (cnt == 0) continue;
-      uint8_t* im = img + q * img_stride;
-      const int tbase = q * N;
-      const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
-      for (int i = threadIdx.x; i < cnt * G; i += blockDim.x) {
-        const int gq = i & (G - 1);
-        const float rr = r_s[tbase * G + i];
-        if (rb == 1) {
-          const float safe = fmaxf(scale_s[q * 8 + gq], 1e-8f);
-          float qv = rintf(__fmul_rn(__fdiv_rn(rr, safe), 127.0f));
-          qv = fminf(fmaxf(qv, -127.f), 127.f);
-          im[roff + i] = (uint8_t)(int8_t)(int)qv;
-        } else {
-          // stage the half's bit pattern as a 32-bit word over the radius slot (same thread
-          // read it above); the bytes are laid into the page image after the barrier
-          unsigned short hv;
-          asm volatile("cvt.rn.f16.f32 %0, %1;" : "=h"(hv) : "f"(rr));
-          reinterpret_cast<uint32_t*>(r_s)[tbase * G + i] = (uint32_t)hv;
-        }
+      if (tin >= cnt) continue;
+      const float rr = r_s[i];
+      if (rb == 1) {
+        const float safe = fmaxf(scale_s[q * 8 + gq], 1e-8f);
+        float qv = rintf(__fmul_rn(__fdiv_rn(rr, safe), 127.0f));
+        qv = fminf(fmaxf(qv, -127.f), 127.f);
+        img[q * img_stride + hdr + ((cnt * G * bits + 7) >> 3) + tin * G + gq] = (uint8_t)(int8_t)(int)qv;
+      } else {
+        // stage the half's bit pattern as a 32-bit word over the radius slot (same thread
+        // read it above); the bytes are laid into the page image after the barrier
+        unsigned short hv;
+        asm volatile("cvt.rn.f16.f32 %0, %1;" : "=h"(hv) : "f"(rr));
+        reinterpret_cast<uint32_t*>(r_s)[i] = (uint32_t)hv;
       }
     }
     if (rb == 2) {
       __syncthreads();
-      for (int q = 0; q < ppb; ++q) {
+      const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_s);
+      for (int b2 = threadIdx.x; b2 < 2 * TB * G; b2 += blockDim.x) {
+        const int i = b2 >> 1;
+        const int ts = i >> g_shift, gq = i & (G - 1);
+        const int q = ts >> n_shift, tin = ts & (N - 1);
         const int cnt = count_s[q];
-        if (cnt == 0) continue;
-        uint8_t* im = img + q * img_stride;
-        const int tbase = q * N;
-        const int roff = 8 + 4 * G + ((cnt * G * bits + 7) >> 3);
-        const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_s + tbase * G);
-        for (int b = threadIdx.x; b < 2 * cnt * G; b += blockDim.x)
-          im[roff + b] = hb[(b >> 1) * 4 + (b & 1)];
+        if (tin >= cnt) continue;
+        img[q * img_stride + hdr + ((cnt * G * bits + 7) >> 3) + 2 * (tin * G + gq) + (b2 & 1)] = hb[i * 4 + (b2 & 1)];
       }
     }
     __syncthreads();
     // ---- copy page images out -------------------------------------------------------------------
-    for (int q = 0; q < ppb; ++q) {
-      const int cnt = count_s[q];
-      if (cnt == 0) continue;
-      const int page = page_s[q];
-      const uint8_t* im = img + q * img_stride;
-      const int bytes = 8 + 4 * G + ((cnt * G * bits + 7) >> 3) + cnt * G * rb;
-      uint8_t* dst = p.k_pages + p.ptable[3 * (int64_t)page];
-      const int words = bytes >> 2;
-      for (int w = threadIdx.x; w < words; w += blockDim.x)
-        reinterpret_cast<uint32_t*>(dst)[w] = reinterpret_cast<const uint32_t*>(im)[w];
-      if ((int)threadIdx.x < (bytes & 3)) dst[words * 4 + threadIdx.x] = im[words * 4 + threadIdx.x];
+    {
+      const int max_img_words = img_stride >> 2;
+      for (int it = threadIdx.x; it < ppb * max_img_words; it += blockDim.x) {
+        const int q = it / max_img_words, w = it - q * max_img_words;
+        const int cnt = count_s[q];
+        if (cnt == 0) continue;
+        const int bytes = hdr + ((cnt * G * bits + 7) >> 3) + cnt * G * rb;
+        if (w < (bytes >> 2))
+          reinterpret_cast<uint32_t*>(p.k_pages + poff_s[q])[w] =
+              reinterpret_cast<const uint32_t*>(img + q * img_stride)[w];
+      }
+      if ((int)threadIdx.x < 4 * ppb) {
+        const int q = threadIdx.x >> 2, t = threadIdx.x & 3;
+        const int cnt = count_s[q];
+        if (cnt > 0) {
+          const int bytes = hdr + ((cnt * G * bits + 7) >> 3) + cnt * G * rb;
+          if (t < (bytes & 3)) p.k_pages[poff_s[q] + (bytes & ~3) + t] = img[q * img_stride + (bytes & ~3) + t];
+        }
+      }
     }
 
     // ---- dense V pages (16-bit), empty slots zero-filled ----------------------------------------
@@ -645,7 +660,7 @@ static int encode_impl(const sphkv_encode_params* pp, void* stream, bool from_co
   for (int s = 0; s < p.tiers.n_slots; ++s) {
     const int G = p.dh / p.tiers.g[s];
     const int img = ((8 + 4 * G + (N * G * p.tiers.bits[s] + 7) / 8 + N * G * 2) + 15) & ~15;
-    const int need = p.dh * p.tiers.C_max * 4 + TB * G * 4 + 64 * 4 + 64 + TB * G + 16 + ppb * img;
+    const int need = p.dh * p.tiers.C_max * 4 + TB * G * 4 + 64 * 4 + 96 + TB * G + 16 + ppb * img;
     smem_bytes = need > smem_bytes ? need : smem_bytes;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
