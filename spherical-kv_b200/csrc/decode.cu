@@ -1057,7 +1057,11 @@ static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st)
     }
     // Ask for the smallest shared-memory carve-out that holds this CTA (plus the 1 KB the system
     // reserves): what is left of the 256 KB array is L1, which serves the cos/sin table rows.
-    const int pct = (int)(((int64_t)smem_bytes + 1024) * 100 / (228 * 1024)) + 1;
+    // The hint is a percentage of 228 KB that the driver rounds UP to a supported size, so it is
+    // rounded down here (the driver never goes below what the launch needs).
+    cudaFuncAttributes fa;
+    const int64_t stat = cudaFuncGetAttributes(&fa, kern) == cudaSuccess ? (int64_t)fa.sharedSizeBytes : 0;
+    const int pct = (int)(((int64_t)smem_bytes + stat + 1024) * 100 / (228 * 1024));
     cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, pct > 100 ? 100 : pct);
     configured_for = smem_bytes;
   }
