@@ -18,7 +18,6 @@ from __future__ import annotations
 import argparse
 import importlib
 import json
-import math
 import os
 import subprocess
 import sys

@@ -5,12 +5,12 @@ from __future__ import annotations
 
 import ctypes as C
 import math
-from typing import Optional, Sequence, Tuple
+from typing import Optional
 
 import torch
 
 from . import _lib
-from .pages import PagedCache, PageLists, TierSet, build_page_lists
+from .pages import PagedCache, PageLists, TierSet
 
 _DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 

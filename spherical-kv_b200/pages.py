@@ -16,7 +16,7 @@ decode arithmetic lives in the CUDA library.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence
 
 import torch
 

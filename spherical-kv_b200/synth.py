@@ -6,11 +6,11 @@ GPU see identical bits.
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Sequence, Tuple
+from typing import Dict, Sequence
 
 import torch
 
-from .pages import REFERENCE_TIERS, TierSet, TierSpec
+from .pages import TierSpec
 
 
 def hf_inv_freq(dh: int, base: float = 500000.0) -> torch.Tensor:
