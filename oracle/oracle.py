@@ -7,8 +7,10 @@ Each function restates one piece of the reference (Anay21013/Spherical-KV) and c
 file:line it follows.  Encode / page bytes go through the C restatement
 (oracle/sphkv_oracle.c, fixed fp32 operation order); decode math is torch on the CPU,
 op for op as the reference's torch path.  The oracle is pinned against outputs of the
-reference itself by the fixtures under tests/golden/ (tests/golden/make_golden.py runs
-the reference; tests/test_oracle_golden.py checks this module against them).
+reference itself by the fixtures under tests/golden/ (make_golden.py, make_golden_pool.py and
+make_golden_kmeans.py there run the reference; tests/test_oracle_golden.py checks this module
+against them).  oracle/build_ref.py additionally compiles the reference's own CUDA kernels as
+a second checker for the LayerPool-format operators.
 """
 from __future__ import annotations
 
