@@ -40,11 +40,15 @@ def kmeans_assign(U: torch.Tensor, centers: torch.Tensor, want_sim: bool = True
 
 
 def spherical_kmeans(U: torch.Tensor, K: int, niter: int, nredo: int, seed: int = 42,
-                     init_centers: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, float]:
+                     init_centers: Optional[torch.Tensor] = None, assign_fn=None) -> Tuple[torch.Tensor, float]:
     """spherical_kmeans_gpu (codebooks/generate.py:31-75) on unit vectors U [N, d].
 
     `init_centers` ([nredo, K, d]) replaces the randperm initialisation (tests feed the
-    reference's own starting points through it; random streams differ between devices)."""
+    reference's own starting points through it; random streams differ between devices).
+    `assign_fn(U, centers, want_sim)` replaces the kernel call; it exists so that the loop around
+    the kernel (restarts, convergence test, scoring) can be exercised without a GPU -- the
+    library itself always runs the kernel."""
+    assign = assign_fn or kmeans_assign
     N, d = U.shape
     if N < K:
         U = U.repeat((K + N - 1) // N, 1)[:K]
@@ -60,7 +64,7 @@ def spherical_kmeans(U: torch.Tensor, K: int, niter: int, nredo: int, seed: int 
             centers = F.normalize(U[idx].clone(), dim=1)
         prev = None
         for _ in range(niter):
-            assigns, _, sums, counts = kmeans_assign(U, centers, want_sim=False)
+            assigns, _, sums, counts = assign(U, centers, want_sim=False)
             if prev is not None and torch.equal(assigns, prev):
                 break
             prev = assigns
@@ -69,7 +73,7 @@ def spherical_kmeans(U: torch.Tensor, K: int, niter: int, nredo: int, seed: int 
             # zero vector.  Same here, so that both produce the same codebooks.
             new_c = sums / counts.float().clamp(min=1).unsqueeze(1)
             centers = F.normalize(new_c, dim=1)
-        _, sim, _, _ = kmeans_assign(U, centers)
+        _, sim, _, _ = assign(U, centers, want_sim=True)
         score = sim.mean().item()
         if score > best_score:
             best_score, best_centers = score, centers.clone()

@@ -160,3 +160,22 @@ def test_pool_page_planner_matches_reference_tables():
     covered = np.concatenate([np.arange(r0, r0 + n) for r0, n in desc[:, :2]])
     np.testing.assert_array_equal(covered, np.arange(total))
     assert sphkv_lut.make_tier_idx_map([type("T", (), {"tier_id": i})() for i in (0, 1, 2, 3)]) == {1: 0, 2: 1, 3: 2}
+
+
+def test_kmeans_training_loop_host_logic_matches_reference():
+    """the loop around the assignment kernel (restarts, convergence break, empty-cluster
+    behaviour, scoring, best-of-restarts) with the kernel replaced by the CPU restatement of
+    one step: ends at the reference's centres and score bit for bit (golden fixture)"""
+    orc = load_oracle()
+    z = np.load(os.path.join(ROOT, "tests", "golden", "kmeans.npz"))
+
+    def cpu_assign(U, centers, want_sim=True):
+        a, best, sums, counts, _ = orc.kmeans_step(U, centers)
+        return a, (best if want_sim else None), sums, counts
+
+    for name in ("g16", "g32", "tiny"):
+        N, d, K, niter, nredo = (int(x) for x in z[f"{name}_cfg"])
+        centers, score = pkg.spherical_kmeans(torch.from_numpy(z[f"{name}_U"]), K, niter, nredo, seed=42,
+                                              init_centers=torch.from_numpy(z[f"{name}_init"]), assign_fn=cpu_assign)
+        np.testing.assert_array_equal(centers.numpy(), z[f"{name}_centers"])
+        assert abs(score - float(z[f"{name}_score"])) <= 1e-7
