@@ -298,6 +298,13 @@ def pool_decode(q_all, cb_flat, tier_G, tier_g, theta_codes, radius_codes, r_sca
     return out, partial
 
 
+def _roundf_nonneg(v) -> np.float32:
+    """C roundf (half away from zero) of a non-negative float32.  The sum v + 0.5 is formed in
+    double, where it is exact: in float32 it can round up to the next integer by itself
+    (0.49999997f + 0.5f == 1.0f), which roundf does not do."""
+    return np.float32(np.floor(np.float64(v) + 0.5))
+
+
 def pool_encode_append(k_post, v_new, decode_cb, theta_codes, radius_codes, r_scales, v_pool, pids,
                        slot: int, G: int, g: int, Cn: int, is_new_page: bool):
     """sphkv_encode_append_kernel (decode_kernel.cu:10-84) on the CPU, in place."""
@@ -332,14 +339,14 @@ def pool_encode_append(k_post, v_new, decode_cb, theta_codes, radius_codes, r_sc
                     for t in range(slot):
                         old = f(radius_codes[pid, t, grp].item())
                         v = f(old * ratio)
-                        v = f(np.floor(v + f(0.5)))  # roundf: half away from zero (v >= 0)
+                        v = _roundf_nonneg(v)
                         radius_codes[pid, t, grp] = int(min(max(v, 0), 255))
                     r_scales[pid, grp] = float(norm)
                     scale = norm
                 else:
                     scale = prev
             rq = f(f(norm / f(scale + f(1e-8))) * f(255.0))
-            rq = f(np.floor(rq + f(0.5)))
+            rq = _roundf_nonneg(rq)
             radius_codes[pid, slot, grp] = int(min(max(rq, 0), 255))
 
 

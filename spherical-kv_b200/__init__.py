@@ -12,11 +12,11 @@ from ._lib import SphKVError, RADIUS_F16, RADIUS_I8  # noqa: F401
 from .pages import (PagedCache, PageLists, REFERENCE_TIERS, TierSet, TierSpec,  # noqa: F401
                     build_page_lists, shard_block_lists)
 from . import split_kv  # noqa: F401
-from .ops import (CodeCache, decode_paged, decode_scratch, encode_codes, encode_pages,  # noqa: F401
+from .ops import (CodeCache, check_status, decode_paged, decode_scratch, encode_codes, encode_pages,  # noqa: F401
                   hf_inv_freq, merge_partials, omega_ema, pages_from_codes, rope_table)
 from .kmeans import kmeans_assign, spherical_kmeans  # noqa: F401
 
 __all__ = ["SphKVError", "RADIUS_F16", "RADIUS_I8", "PagedCache", "PageLists", "REFERENCE_TIERS",
-           "TierSet", "TierSpec", "build_page_lists", "shard_block_lists", "decode_paged", "decode_scratch",
+           "TierSet", "TierSpec", "build_page_lists", "shard_block_lists", "check_status", "decode_paged", "decode_scratch",
            "encode_pages", "hf_inv_freq", "merge_partials", "omega_ema", "rope_table", "kmeans_assign", "CodeCache", "encode_codes", "pages_from_codes",
            "spherical_kmeans"]

@@ -16,7 +16,7 @@ F32, BF16, F16 = 0, 1, 2
 RADIUS_I8, RADIUS_F16 = 0, 1
 MAX_TIER_SLOTS = 4
 MAX_GQA = 8
-ST_BAD_POSITION, ST_BAD_BLOCK, ST_BAD_SLOT = 1, 2, 4
+ST_BAD_POSITION, ST_BAD_BLOCK, ST_BAD_SLOT, ST_TIMEOUT, ST_INTERNAL = 1, 2, 4, 8, 16
 
 _I4 = C.c_int32 * MAX_TIER_SLOTS
 

@@ -33,6 +33,19 @@ void set_error(const char* fmt, ...);
     }                                  \
   } while (0)
 
+// ---- per-device host state ---------------------------------------------------------
+// The SM count and a kernel's dynamic shared-memory opt-in belong to a device, not to the
+// process, so what the host caches about them is indexed by the current device.
+constexpr int kMaxDevices = 64;
+int current_device_slot();      // cudaGetDevice(), or -1 when it fails / index >= kMaxDevices
+int sm_count_current_device();  // > 0, or a negative error
+struct SmemOptIn {
+  int bytes[kMaxDevices];  // largest size this kernel was opted in for, per device (0 = never)
+};
+// Raises `kernel`'s dynamic shared-memory limit on the current device to `bytes` if it is not
+// there yet.  Sizes up to 48 KB need no opt-in and are not recorded.
+int ensure_dynamic_smem(SmemOptIn& st, const void* kernel, int bytes, const char* what);
+
 inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

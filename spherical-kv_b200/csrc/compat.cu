@@ -365,8 +365,7 @@ __global__ void ragged_logits_kernel(const uint8_t* __restrict__ pages,
 using namespace sphkv;
 
 static int sphkv_sm_count_or(int fallback) {
-  static int sms = 0;
-  if (sms <= 0) sms = sphkv_sm_count();
+  const int sms = sm_count_current_device();
   return sms > 0 ? sms : fallback;
 }
 
@@ -397,15 +396,9 @@ extern "C" int sphkv_pool_decode(const float* q_all, const float* cb_flat, const
   const size_t smem = ((size_t)kv_groups * dh + (size_t)num_tiers * kv_groups * G_max * cb_max +
                        (size_t)kPoolWarps * ((size_t)kv_groups * page_size + G_max)) * sizeof(float);
   SPHKV_REQUIRE(smem <= 200 * 1024, SPHKV_E_LIMIT, "pool_decode: needs %zu B shared memory", smem);
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(pool_page_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      set_error("pool_decode: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      return (int)e;
-    }
-    configured = smem;
+  {
+    static SmemOptIn opt_in;
+    if (int rc = ensure_dynamic_smem(opt_in, (const void*)pool_page_kernel, (int)smem, "pool_decode")) return rc;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // pages per warp: up to kMaxPagesPerWarp (amortises the table build), fewer while the grid is small
@@ -563,15 +556,10 @@ extern "C" int sphkv_omega_ema(const float* ml, float* omega, int32_t n_units, i
   SPHKV_REQUIRE((size_t)max_blocks * 4 <= 160 * 1024, SPHKV_E_LIMIT,
                 "omega_ema: max_blocks=%d exceeds 40960", max_blocks);
   const size_t smem = (size_t)max_blocks * 4;
-  static size_t configured = 48 * 1024;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(sphkv::omega_ema_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-      sphkv::set_error("omega_ema: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-      return (int)e;
-    }
-    configured = smem;
+  {
+    static sphkv::SmemOptIn opt_in;
+    if (int rc = sphkv::ensure_dynamic_smem(opt_in, (const void*)sphkv::omega_ema_kernel, (int)smem, "omega_ema"))
+      return rc;
   }
   sphkv::omega_ema_kernel<<<n_units, 256, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
       ml, omega, kv_groups, max_blocks, stride, beta);

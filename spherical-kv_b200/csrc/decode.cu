@@ -1,23 +1,31 @@
 // Angle-domain decode attention over bit-packed, paged, codebook-quantised keys.
 //
-// One persistent CTA per SM (12 warps) walks a contiguous range of (KV head, batch row)
-// blocks.  Each warp owns every 12th 16-token tile of the range and keeps an online-softmax
-// state for all query heads of the KV head.  Per tile a warp
-//   1. unpacks the tile's centroid indices and radii (lane = token x half of the groups),
-//   2. rebuilds the 16 x dh key tile directly in mma A-fragment registers: gathers the
-//      selected centroid rows from shared memory, scales by the radius and rotates by the
-//      key's RoPE angle (cos/sin row of the key position, read through L2),
-//   3. forms logits with fp16 hi/lo split operands on the tensor cores
-//      (tokens x dh) * (dh x heads), fp32 accumulate,
-//   4. runs the online softmax and accumulates V^T P^T with V tiles that cp.async streams
-//      into a swizzled shared-memory ring.
-// Every global load a tile needs is issued one or two tiles ahead.  Warp states are merged
-// per CTA, CTA partials land in scratch, and a small kernel merges them by log-sum-exp.
+// One persistent CTA per SM walks a contiguous range of (KV head, batch row) blocks.  Each
+// warp owns every kWarps-th 16-token tile of the range and keeps an online-softmax state for
+// all query heads of the KV head.
+//
+// Lane map of a tile (lane = 4 r + j): rows r and r + 8 are the lane's two tokens; in each
+// rotary half the lane owns the contiguous block of W = dh / 8 dimensions  W j .. W j + W - 1
+// and, in the other half, the same block shifted by dh / 2 -- the RoPE partner of every value
+// a lane holds is in the same lane, and for g = 16, dh = 128 a lane needs exactly two centroid
+// indices and two radii per token, which it extracts itself from the page bytes.  Per tile a warp
+//   1. reads its code / radius words straight from the page (issued one tile earlier),
+//   2. gathers the selected centroid rows from shared memory (128-bit loads, chunk order
+//      skewed by j so the four lanes of a token never meet in a bank), scales by the radius
+//      and rotates by the key's RoPE angle; the cos/sin rows of the key positions arrive in
+//      shared memory by bulk async copies issued half a tile ahead,
+//   3. feeds the rotated values to the tensor cores as TF32 hi + lo parts
+//      (tokens x dh) * (dh x heads), fp32 accumulate, query fragments held in registers,
+//   4. runs the online softmax and accumulates V^T P^T; V tiles are fetched by the tensor
+//      memory accelerator (2-D tiled copies with the 128-byte swizzle ldmatrix wants).
+// Warp states are merged per CTA, CTA partials land in scratch, and a small kernel merges
+// them by log-sum-exp.
 //
 // Numerics restate SphericalKVPipeline._compressed_head_attention_batched
 // (spherical_kv_pipeline.py:2136-2177): logit = sum_g r_g * (q_rot_g . c_g) / sqrt(dh)
 // with q back-rotated by the key position; rotating the rebuilt key forward instead is the
 // same bilinear form.  Page bytes follow pagebuilder.py:8-33 / paging.py:20-31.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder is looked up at run time (no -lcuda)
 #include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -29,28 +37,31 @@
 namespace sphkv {
 
 #ifndef SPHKV_WARPS
-#define SPHKV_WARPS 12
-#endif
-#ifndef SPHKV_CB_DUP
-#define SPHKV_CB_DUP 0  // 1: store every codebook sub-row twice (bank-conflict-free gathers; measured slower)
+#define SPHKV_WARPS 8
 #endif
 constexpr int kWarps = SPHKV_WARPS;
-constexpr int kCbPitch = SPHKV_CB_DUP ? 128 : 64;  // bytes per 16-dim codebook sub-row slot
 #ifndef SPHKV_VSTAGES
-#define SPHKV_VSTAGES 2
+#define SPHKV_VSTAGES 3
 #endif
-constexpr int kVStages = SPHKV_VSTAGES;  // V tiles in flight per warp: tile k + kVStages - 1 is
-                                         // copied while tile k is consumed, so >= 2
-static_assert(kVStages >= 2, "the V ring needs a stage to fill while another is read");
+constexpr int kVStages = SPHKV_VSTAGES;  // V tile buffers per warp: one being read, the others in flight
 constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
 constexpr int kMaxUnitsInKernelPlan = 2048;
-
-// kernel-development switch: compile sections of the tile loop out to count their
-// instructions (results are wrong when non-zero); 0 in every shipped build
-#ifndef SPHKV_X_SKIP
-#define SPHKV_X_SKIP 0
+// operand split of the QK^T contraction: 2 = TF32 hi + lo (m16n8k8), 1 = bf16 hi + lo by
+// truncation (m16n8k16)
+#ifndef SPHKV_SPLIT
+#define SPHKV_SPLIT 2
 #endif
-constexpr int kSkip = SPHKV_X_SKIP;
+constexpr int kSplit = SPHKV_SPLIT;
+// cos/sin rows: 1 = bulk async copies into shared memory, 0 = 128-bit loads into registers
+#ifndef SPHKV_CS_STAGED
+#define SPHKV_CS_STAGED 1
+#endif
+constexpr bool kCsStaged = SPHKV_CS_STAGED != 0;
+// second, bank-disjoint copy of a g = 16 codebook for odd token rows: 0 never, 1 for
+// slots of at most 16 centroids, 2 for every slot that fits
+#ifndef SPHKV_CB_DUP
+#define SPHKV_CB_DUP 1
+#endif
 
 // 16 bytes per tile
 struct TileMeta {
@@ -64,8 +75,10 @@ __device__ __forceinline__ int meta_slot(const TileMeta& m) { return (m.misc >> 
 __device__ __forceinline__ int meta_roff(const TileMeta& m) { return m.toff + (int)(m.misc & 0xFFFF); }
 
 struct DecodeArgs {
+  alignas(64) CUtensorMap v_map;  // V pool as [pages * page_size rows][dh], 16 x 64 boxes, 128-byte swizzle
   sphkv_decode_params p;
   int cb_smem_off[SPHKV_MAX_TIER_SLOTS];  // byte offset of each slot's codebook in smem
+  int cb_dup[SPHKV_MAX_TIER_SLOTS];       // 1: two copies at a 128-byte row pitch
   int cb_smem_bytes;
   int n_units;
   int n_ctas;
@@ -77,16 +90,104 @@ struct DecodeArgs {
 
 // shared-memory carve-up, shared by host and device
 __host__ __device__ constexpr int smem_v_bytes(int dh) { return kWarps * kVStages * 16 * dh * 2; }
-// query fragments: hi and lo copies, or one copy when both halves share the 8 MMA columns (packed)
-__host__ __device__ constexpr int smem_q_bytes(int dh, bool pack) { return (pack ? 1 : 2) * (dh / 16) * 32 * 8; }
-__host__ __device__ constexpr int smem_priv_bytes(int dh) {
-  return 16 * (dh / 16) * 8 + 512 + kMetaRing * 16;
-}
+// one half of a cos/sin row (dh * 2 bytes) per token, 16 bytes of padding so that the two
+// tokens a quarter-warp reads sit in different banks
+__host__ __device__ constexpr int cs_pitch(int dh) { return dh * 2 + 16; }
+__host__ __device__ constexpr int smem_cs_bytes(int dh) { return kCsStaged ? kWarps * 2 * 16 * cs_pitch(dh) : 0; }
+// per warp: P^T buffer, tile metadata ring, mbarriers (kVStages for V, two for cos/sin)
+__host__ __device__ constexpr int smem_priv_bytes() { return 512 + kMetaRing * 16 + 64; }
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// ---- mbarrier / bulk-copy wrappers (inline PTX) ----------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait: the copies a warp waits for are its own, so a phase that does not complete
+// within about a second means a lost copy; the caller then raises a status bit and the
+// warp stops working instead of spinning for ever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > 2000000000LL) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// one row segment, global -> this CTA's shared memory, completion counted on an mbarrier
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// one box of a 2-D tensor map, global -> this CTA's shared memory
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// ---- RoPE table ------------------------------------------------------------------------
+// Row of one position: for loop index i (0 .. W/4 - 1) and lane quad member j (0 .. 3) the
+// four frequencies  W j + 4 ((i + j) mod (W/4)) + {0..3}  as {cos x 4, sin x 4}: 32 bytes per
+// (i, j), so what the four lanes of a token read in one step is one 128-byte line, and the
+// first half of the row is what the first half of the tile loop needs.
+__host__ __device__ __forceinline__ int lane_freq(int dh, int i, int j, int e) {
+  const int W = dh / 8, nch = W / 4;
+  return W * j + 4 * ((i + j) & (nch - 1)) + e;
+}
+__global__ void rope_table_kernel(float* __restrict__ table, int max_pos, int dh,
+                                  const float* __restrict__ inv_freq) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int half = dh / 2;
+  if (idx >= (int64_t)max_pos * half) return;
+  const int pos = (int)(idx / half), q = (int)(idx - (int64_t)pos * half);
+  const int e = q & 3, j = (q >> 2) & 3, i = q >> 4;
+  const int f = lane_freq(dh, i, j, e);
+  const float ang = __fmul_rn((float)pos, inv_freq[f]);
+  double sn, cs;
+  sincos((double)ang, &sn, &cs);
+  float* row = table + (int64_t)pos * dh + (i * 4 + j) * 8;
+  row[e] = (float)cs;
+  row[4 + e] = (float)sn;
 }
 
 // ---- plan: exclusive prefix of blocks per unit --------------------------------------
@@ -145,174 +246,72 @@ __device__ __forceinline__ int find_unit(const int32_t* pfx, int n, int64_t x) {
   return lo;
 }
 
-// words of a K page this lane needs for its (token, half-of-groups) unpack role
-struct KWords {
-  uint32_t th0, th1;       // aligned words holding this lane's theta bits
-  uint32_t rd0, rd1, rd2;  // aligned words holding this lane's radius bytes
-  float sc[4];             // per-group scales of this lane's groups
-  int th_sh, rd_sh;        // bit shifts into the funnels
+// Page words a lane needs for its two tokens (index = 2 * token + rotary half): the aligned
+// 32-bit word holding the start of the centroid index (and the next one when the index
+// straddles it), the word(s) holding the radius, and the two per-group scales.
+// The positions of the two tokens ride along.  Three of these rotate through the tile loop
+// (tile k is consumed while the loads of tiles k + 1 and k + 2 are in flight); the loop is
+// unrolled by three so that each set keeps its registers: copying a set forward would make
+// every iteration wait for loads it has only just issued.
+struct KRaw {
+  uint32_t tw0[4], tw1[4], rw0[4], rw1[4];
+  float sc[2];
+  int pos[2];
 };
 
-// Issue the global loads of one lane's K words.  SPG = 16-dim steps per group (g / 16).
-template <int DH, int SPG>
-__device__ __forceinline__ void load_kwords_t(const sphkv_decode_params& p, const TileMeta& m, int sub,
-                                              int bits, int ut, int uhalf, KWords& w) {
-  constexpr int HS = DH / 32, NG = HS / SPG, G = DH / (16 * SPG);
-  const int tp = 16 * sub + ut;
-  if (tp >= meta_count(m)) return;
-  const int gam0 = uhalf * NG;
-  const int bit = (tp * G + gam0) * bits;
-  const int ba = m.toff + (bit >> 3);
-  const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.k_pages + (ba & ~3));
-  w.th_sh = (ba & 3) * 8 + (bit & 7);
-  w.th0 = wp[0];
-  if (w.th_sh + NG * bits > 32) w.th1 = wp[1];
-  const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-  const int ra = meta_roff(m) + (tp * G + gam0) * rb;
-  const uint32_t* rp = reinterpret_cast<const uint32_t*>(p.k_pages + (ra & ~3));
-  w.rd_sh = (ra & 3) * 8;
-  const int need = (ra & 3) + NG * rb;  // bytes from the aligned word start
-  w.rd0 = rp[0];
-  if (need > 4) w.rd1 = rp[1];
-  if (need > 8) w.rd2 = rp[2];
-  if (rb == 1) {
-    const float* sp = reinterpret_cast<const float*>(p.k_pages + m.poff + 8) + gam0;
-#pragma unroll
-    for (int i = 0; i < NG; ++i) w.sc[i] = sp[i];
-  }
-}
-
-// Unpack this lane's codes and radii into (codebook row offset, radius) entries, one per
-// 16-dim step: unp[token][step].
-template <int DH, int SPG>
-__device__ __forceinline__ void unpack_t(const KWords& w, const TileMeta& m, int sub, int bits, int fmt,
-                                         uint32_t cbase, int ut, int uhalf, uint2* unp) {
-  constexpr int KS = DH / 16, HS = KS / 2, NG = HS / SPG;
-  const int gam0 = uhalf * NG;
-  const uint32_t cmask = (1u << bits) - 1u;
-  const uint32_t tb = __funnelshift_r(w.th0, w.th1, w.th_sh);
-  const uint32_t rlo = __funnelshift_r(w.rd0, w.rd1, w.rd_sh);
-  const uint32_t rhi = __funnelshift_r(w.rd1, w.rd2, w.rd_sh);
-  const bool tok_ok = (16 * sub + ut) < meta_count(m);
-  uint2 e[NG * SPG];
-#pragma unroll
-  for (int i = 0; i < NG; ++i) {
-    const uint32_t code = (tb >> (i * bits)) & cmask;
-    float rad;
-    if (fmt == SPHKV_RADIUS_F16) {
-      const uint32_t wv = (i < 2) ? rlo : rhi;
-      rad = __half2float(__ushort_as_half((unsigned short)(wv >> ((i & 1) * 16))));
-    } else {
-      const int c8 = (int)(int8_t)((rlo >> (i * 8)) & 0xFFu);
-      rad = (w.sc[i] * (float)c8) * (1.0f / 127.0f);
-    }
-    if (!tok_ok) rad = 0.f;
-    const uint32_t row = (((uint32_t)(gam0 + i) << bits) + code) * SPG;
-#pragma unroll
-    for (int s2 = 0; s2 < SPG; ++s2)
-      e[i * SPG + s2] = make_uint2(cbase + (row + s2) * (uint32_t)kCbPitch, __float_as_uint(rad));
-  }
-  uint2* dst = unp + ut * KS + gam0 * SPG;  // 16-byte aligned: KS and NG*SPG are even
-#pragma unroll
-  for (int i = 0; i < NG * SPG; i += 2)
-    *reinterpret_cast<uint4*>(dst + i) = make_uint4(e[i].x, e[i].y, e[i + 1].x, e[i + 1].y);
-}
-
-// rotate one (low-half, high-half) float4 pair by (cos, sin) and split into fp16 hi/lo
-// A-fragment registers
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
-
-// Operand precision of the QK^T contraction: both the rebuilt key tile and the query are
-// split as hi + lo 16-bit halves and three products are accumulated in fp32
-// (hi*hi + lo*hi + hi*lo).  SPHKV_SPLIT_BF16: bf16 halves (hi by truncation, no conversion
-// instructions on the slow pipe; ~2^-16 relative); otherwise fp16 halves (~2^-21).
-#ifdef SPHKV_SPLIT_BF16
-__device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo) {
-  const uint32_t a = __float_as_uint(v.x), b = __float_as_uint(v.y);
-  hi = __byte_perm(a, b, 0x7632);  // upper halves = truncated bf16 pair
-  const float2 nh = f2(__uint_as_float((a & 0xFFFF0000u) ^ 0x80000000u),
-                       __uint_as_float((b & 0xFFFF0000u) ^ 0x80000000u));
-  const float2 l = __fadd2_rn(v, nh);
-  __nv_bfloat162 lb = __floats2bfloat162_rn(l.x, l.y);
-  lo = *reinterpret_cast<uint32_t*>(&lb);
-}
-#define SPHKV_QK_MMA mma_bf16_16816
-#else
-__device__ __forceinline__ void split_pair(float2 v, uint32_t& hi, uint32_t& lo) {
-  split_f16x2(v.x, v.y, hi, lo);
-}
-#define SPHKV_QK_MMA mma_f16_16816
-#endif
-
-// rotate one (low-half, high-half) float4 pair by (cos, sin) and split into hi/lo
-// A-fragment registers
-template <bool ROT>
-__device__ __forceinline__ void build_pair(float4 x, float4 y, float r0, float r1, const float4& c,
-                                           const float4& sn, int tk, uint32_t (&a_lo_hi)[4],
-                                           uint32_t (&a_lo_lo)[4], uint32_t (&a_hi_hi)[4],
-                                           uint32_t (&a_hi_lo)[4]) {
-#ifndef SPHKV_NO_F32X2
-  const float2 rr0 = f2(r0, r0), rr1 = f2(r1, r1);
-  float2 x0 = __fmul2_rn(f2(x.x, x.y), rr0), x1 = __fmul2_rn(f2(x.z, x.w), rr0);
-  float2 y0 = __fmul2_rn(f2(y.x, y.y), rr1), y1 = __fmul2_rn(f2(y.z, y.w), rr1);
-  float2 lo0 = x0, lo1 = x1, hi0 = y0, hi1 = y1;
-  if (ROT) {
-    const float2 c0 = f2(c.x, c.y), c1 = f2(c.z, c.w);
-    const float2 s0 = f2(sn.x, sn.y), s1 = f2(sn.z, sn.w);
-    const float2 n0 = f2(-sn.x, -sn.y), n1 = f2(-sn.z, -sn.w);
-    lo0 = __ffma2_rn(y0, n0, __fmul2_rn(x0, c0));
-    lo1 = __ffma2_rn(y1, n1, __fmul2_rn(x1, c1));
-    hi0 = __ffma2_rn(x0, s0, __fmul2_rn(y0, c0));
-    hi1 = __ffma2_rn(x1, s1, __fmul2_rn(y1, c1));
-  }
-#else
-  x.x *= r0; x.y *= r0; x.z *= r0; x.w *= r0;
-  y.x *= r1; y.y *= r1; y.z *= r1; y.w *= r1;
-  float2 lo0 = f2(x.x, x.y), lo1 = f2(x.z, x.w), hi0 = f2(y.x, y.y), hi1 = f2(y.z, y.w);
-  if (ROT) {
-    lo0.x = fmaf(x.x, c.x, -(y.x * sn.x)); hi0.x = fmaf(y.x, c.x, x.x * sn.x);
-    lo0.y = fmaf(x.y, c.y, -(y.y * sn.y)); hi0.y = fmaf(y.y, c.y, x.y * sn.y);
-    lo1.x = fmaf(x.z, c.z, -(y.z * sn.z)); hi1.x = fmaf(y.z, c.z, x.z * sn.z);
-    lo1.y = fmaf(x.w, c.w, -(y.w * sn.w)); hi1.y = fmaf(y.w, c.w, x.w * sn.w);
-  }
-#endif
-  split_pair(lo0, a_lo_hi[tk], a_lo_lo[tk]);
-  split_pair(lo1, a_lo_hi[2 + tk], a_lo_lo[2 + tk]);
-  split_pair(hi0, a_hi_hi[tk], a_hi_lo[tk]);
-  split_pair(hi1, a_hi_hi[2 + tk], a_hi_lo[2 + tk]);
-}
 
 // PACK (<= 4 query heads per KV head): the 8 mma columns carry [q_hi heads 0..3 | q_lo heads
 // 0..3] (one product fewer per step) and later [P_hi | P_lo] (one product per V tile).
 template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
-__global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const DecodeArgs a) {
-  constexpr int KS = DH / 16;  // 16-dim steps over the head dim
-  constexpr int HS = KS / 2;   // steps in one rotary half
+__global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
+  constexpr int KS = DH / 16;   // 16-dim output tiles of the V product
+  constexpr int W = DH / 8;     // dims a lane owns in each rotary half
+  constexpr int NCH = W / 4;    // 16-byte chunks of those dims
+  constexpr int NH = NCH / 2;   // chunks per half of the tile loop
   constexpr int V_TILE = 16 * DH * 2;
   constexpr int V_WARP = kVStages * V_TILE;
+  constexpr int CS_PITCH = cs_pitch(DH);
+  constexpr int CS_HALF = 16 * CS_PITCH;
   constexpr bool kBf16 = std::is_same<VT, __nv_bfloat16>::value;
+  constexpr bool STAGED = ROT && kCsStaged;
+  // query fragment registers per (rotary half, chunk): TF32 two k8 steps x {b0, b1}, bf16 one k16 step
+  constexpr int QR = kSplit == 2 ? 4 : 2;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   const sphkv_decode_params& p = a.p;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = lane >> 2, j = lane & 3;
-  const int ut = lane >> 1, uhalf = lane & 1;  // unpack role: token, half of the groups
 
   uint8_t* v_ring = smem + warp * V_WARP;
-  uint8_t* cb_smem = smem + smem_v_bytes(DH);
-  const uint8_t* cb_lane = cb_smem + j * 16 + (SPHKV_CB_DUP ? (r & 1) * 64 : 0);  // this lane's chunk of its copy
-  uint2* q_smem = reinterpret_cast<uint2*>(cb_smem + a.cb_smem_bytes);  // [PACK ? 1 : 2][KS][32]
-  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + smem_q_bytes(DH, PACK) + warp * smem_priv_bytes(DH);
-  uint2* unp = reinterpret_cast<uint2*>(warp_priv);                       // [16][KS]
-  uint16_t* pbuf = reinterpret_cast<uint16_t*>(warp_priv + 16 * KS * 8);  // [2][8][16]
-  TileMeta* meta = reinterpret_cast<TileMeta*>(warp_priv + 16 * KS * 8 + 512);
+  uint8_t* cs_warp = smem + smem_v_bytes(DH) + warp * 2 * CS_HALF;
+  uint8_t* cb_smem = smem + smem_v_bytes(DH) + smem_cs_bytes(DH);
+  uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + warp * smem_priv_bytes();
+  uint16_t* pbuf = reinterpret_cast<uint16_t*>(warp_priv);  // [2][8][16]
+  TileMeta* meta = reinterpret_cast<TileMeta*>(warp_priv + 512);
+  const uint32_t bar_v = smem_u32(warp_priv + 512 + kMetaRing * 16);  // one per V stage
+  const uint32_t bar_cs = bar_v + 8 * kVStages;                        // two cos/sin halves
+  static_assert(8 * (kVStages + 2) <= 64, "mbarriers exceed their slot");
+  const uint32_t cb_u32 = smem_u32(cb_smem);
+  const uint32_t cs_lane = smem_u32(cs_warp) + r * CS_PITCH + j * 32;
+
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < kVStages; ++i) mbar_init(bar_v + 8 * i, 1);
+    mbar_init(bar_cs, 1);
+    mbar_init(bar_cs + 8, 1);
+    fence_async_smem();
+  }
+  __syncthreads();
+  // V ring position of the next tile to issue / to wait for: stage index and phase parity
+  uint32_t vi_stage = 0, vw_stage = 0, vw_phase = 0, cs_waited[2] = {0, 0};
+  bool dead = false;  // a bounded wait ran out: stop working, keep meeting the CTA barriers
 
   // ---- block prefix per unit: computed by warp 0 of every CTA (CTA 0 publishes it for the
   //      merge kernel), or read from the plan kernel's output when there are many units ----
   const int32_t* pfx = a.pfx;
   if (a.plan_in_kernel) {
-    int32_t* pfx_s = reinterpret_cast<int32_t*>(cb_smem + a.cb_smem_bytes + smem_q_bytes(DH, PACK) +
-                                                kWarps * smem_priv_bytes(DH));
+    int32_t* pfx_s = reinterpret_cast<int32_t*>(cb_smem + a.cb_smem_bytes + kWarps * smem_priv_bytes());
     if (warp == 0) {
       int carry = 0;
       for (int base = 0; base < a.n_units; base += 32) {
@@ -350,22 +349,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
   int u = find_unit(pfx, a.n_units, start);
 
   const int N = p.page_size;
-  const int TPP = N >> 4;                 // 16-token tiles per page: 1, 2, 4 or 8
+  const int TPP = N >> 4;  // 16-token tiles per page: 1, 2, 4 or 8
   const int tpp_shift = 31 - __clz(TPP);
   const float qscale = p.sm_scale * kLog2e;
   const int fmt = p.radius_fmt;
+  const int rb = fmt == SPHKV_RADIUS_F16 ? 2 : 1;
   int cb_head_loaded = -1;
-  // per tier slot: b_theta | steps-per-group << 8 | codebook offset in shared memory << 12,
-  // held by lanes 0..3 and read with a shuffle (no indexing into kernel parameters)
+  // per tier slot: b_theta | log2(g) << 8 | duplicated << 12 | codebook offset in shared
+  // memory << 13, held by lanes 0..3 and read with a shuffle
   uint32_t tier_word = 0;
   if (lane < SPHKV_MAX_TIER_SLOTS && lane < p.tiers.n_slots) {
-    int g_l = 16, b_l = 1, off_l = 0;
+    int g_l = 16, b_l = 1, off_l = 0, dup_l = 0;
 #pragma unroll
     for (int s = 0; s < SPHKV_MAX_TIER_SLOTS; ++s)
-      if (s == lane) { g_l = p.tiers.g[s]; b_l = p.tiers.bits[s]; off_l = a.cb_smem_off[s]; }
-    tier_word = (uint32_t)b_l | ((uint32_t)(g_l >> 4) << 8) | ((uint32_t)off_l << 12);
+      if (s == lane) { g_l = p.tiers.g[s]; b_l = p.tiers.bits[s]; off_l = a.cb_smem_off[s]; dup_l = a.cb_dup[s]; }
+    tier_word = (uint32_t)b_l | ((uint32_t)(g_l == 32 ? 5 : 4) << 8) | ((uint32_t)dup_l << 12) |
+                ((uint32_t)off_l << 13);
   }
   auto tier_of = [&](int slot) { return __shfl_sync(0xffffffffu, tier_word, slot); };
+  // chunk order of this lane: loop index i reads chunk (i + j) mod NCH of its centroid rows
+  uint32_t coff[NCH];
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) coff[i] = (uint32_t)(((i + j) & (NCH - 1)) * 16);
 
   while (start < end) {
     while ((int64_t)pfx[u + 1] <= start) ++u;  // skip units without blocks
@@ -376,13 +381,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
     // their codebooks; tables are indexed by the external unit id b * Hkv + hkv
     const int hkv = u / p.B, b = u - hkv * p.B;
     const int u_ext = b * p.Hkv + hkv;
-    const int nt = seg_tiles > warp ? (seg_tiles - warp + kWarps - 1) / kWarps : 0;
+    const int nt = (!dead && seg_tiles > warp) ? (seg_tiles - warp + kWarps - 1) / kWarps : 0;
     const int32_t* bt_row = p.block_table + (int64_t)u_ext * p.max_blocks;
     const int32_t* st_row = p.bits_table + (int64_t)u_ext * p.max_blocks;
 
     auto tile_lb = [&](int kk) { return lb0 + ((warp + kWarps * kk) >> tpp_shift); };
     auto tile_sub = [&](int kk) { return (warp + kWarps * kk) & (TPP - 1); };
-    // per-tile statistics of this segment: tile kk of head n lands at ml_seg[n * ml_head + 2 * (warp + 12 kk)]
+    // per-tile statistics of this segment: tile kk of head n lands at ml_seg[n * ml_head + 2 * (warp + kWarps kk)]
     float* ml_seg = nullptr;
     const int64_t ml_head = (int64_t)p.max_blocks * TPP * 2;
     if (EXTRA && p.page_ml != nullptr)
@@ -437,134 +442,209 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
       return m;
     };
 
-    // V tile copy: lane owns 16-byte chunk column c = lane % (DH/8) of token rows
-    // tau = q * (256/DH) + lane / (DH/8); destination chunks are XOR-swizzled by (tau & 7)
+    // V tile kk into the next ring stage: one lane, one or two boxes of 16 rows x 128 bytes
+    // through the tensor map, hardware swizzle = chunk ^ (row & 7)
     auto issue_v = [&](int kk) {
-      if (kk < nt && !(kSkip & 8)) {
-        const TileMeta m = get_meta(kk);
+      if (kk >= nt) return;
+      const TileMeta m = get_meta(kk);
+      if (lane == 0) {
+        const uint32_t bar = bar_v + 8 * vi_stage;
         if (m.phys >= 0) {
-          constexpr int CPR = DH / 8;       // chunks per token row
-          constexpr int RPI = 32 / CPR;     // token rows per warp-wide copy instruction
-          const int c = lane % CPR, t0 = lane / CPR;
-          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.v_pool) +
-                               ((int64_t)m.phys * N + 16 * tile_sub(kk)) * (DH * 2) + t0 * (DH * 2) + c * 16;
-          const uint32_t dst = smem_u32(v_ring) + (uint32_t)(kk % kVStages) * V_TILE + (c >> 3) * 2048 +
-                               t0 * 128;
+          mbar_expect_tx(bar, V_TILE);
+          const uint32_t dst = smem_u32(v_ring) + vi_stage * V_TILE;
+          const int y = m.phys * N + 16 * tile_sub(kk);
 #pragma unroll
-          for (int q = 0; q < 16 / RPI; ++q) {
-            const int tau = q * RPI + t0;
-            cp_async_16(dst + q * RPI * 128 + (((c & 7) ^ (tau & 7)) << 4), src + q * RPI * DH * 2);
+          for (int h = 0; h < DH / 64; ++h) tma_load_2d(dst + h * 2048, &a.v_map, 64 * h, y, bar);
+        } else {
+          mbar_arrive(bar);
+        }
+      }
+      vi_stage = vi_stage + 1 == kVStages ? 0 : vi_stage + 1;
+    };
+    // waits for the oldest tile in flight; returns its stage through `stage`
+    auto wait_v = [&](uint32_t& stage) -> bool {
+      const bool ok = mbar_wait(bar_v + 8 * vw_stage, vw_phase);
+      stage = vw_stage;
+      if (++vw_stage == kVStages) { vw_stage = 0; vw_phase ^= 1u; }
+      return ok;
+    };
+
+    // geometry of this lane's two groups for a tier word
+    auto lane_groups = [&](uint32_t tw, int& G, int& glo, int& ghi, int& sub_off) {
+      const int lg = (tw >> 8) & 0xF;
+      G = DH >> lg;
+      glo = (W * j) >> lg;
+      ghi = glo + (G >> 1);
+      sub_off = (W * j) & ((1 << lg) - 1);
+    };
+
+    auto load_kraw = [&](int kk, KRaw& w) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) w.tw0[i] = w.tw1[i] = w.rw0[i] = w.rw1[i] = 0u;
+      w.sc[0] = w.sc[1] = 0.f;
+      w.pos[0] = w.pos[1] = -1;
+      if (kk >= nt) return;
+      const TileMeta m = get_meta(kk);
+      if (m.phys < 0) return;
+      if (ROT) {  // key positions of rows r and r + 8 (-1: no token)
+        const int32_t* pp = p.positions + (int64_t)m.phys * N + 16 * tile_sub(kk);
+        w.pos[0] = pp[r];
+        w.pos[1] = pp[r + 8];
+      }
+      const uint32_t tw = tier_of(meta_slot(m));
+      const int bits = tw & 0xFF;
+      int G, glo, ghi, sub_off;
+      lane_groups(tw, G, glo, ghi, sub_off);
+      const int roff = meta_roff(m);
+#pragma unroll
+      for (int tk = 0; tk < 2; ++tk) {
+        const int tp = 16 * tile_sub(kk) + r + 8 * tk;
+        if (tp >= meta_count(m)) continue;
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          const int idx = tp * G + (hf ? ghi : glo);
+          const int bit = idx * bits;
+          const int ba = m.toff + (bit >> 3);
+          const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.k_pages + (ba & ~3));
+          w.tw0[2 * tk + hf] = wp[0];
+          if ((ba & 3) * 8 + (bit & 7) + bits > 32) w.tw1[2 * tk + hf] = wp[1];
+          const int ra = roff + idx * rb;
+          const uint32_t* rp = reinterpret_cast<const uint32_t*>(p.k_pages + (ra & ~3));
+          w.rw0[2 * tk + hf] = rp[0];
+          if (rb == 2 && (ra & 3) == 3) w.rw1[2 * tk + hf] = rp[1];
+        }
+      }
+      if (rb == 1) {
+        const float* sp = reinterpret_cast<const float*>(p.k_pages + m.poff + 8);
+        w.sc[0] = sp[glo];
+        w.sc[1] = sp[ghi];
+      }
+    };
+    auto clamp_pos = [&](int pos) -> int {
+      if (pos >= p.max_pos) {
+        if (p.status) atomicOr(p.status, SPHKV_ST_BAD_POSITION);
+        pos = 0;
+      }
+      return pos < 0 ? 0 : pos;
+    };
+
+    // cos/sin of the tile's key positions.  Staged: half h of the row (loop indices
+    // h * NH .. h * NH + NH - 1) of every token goes to shared memory by one bulk copy per
+    // token, lanes with j = 0 for rows r, j = 1 for rows r + 8.  Register path: this lane's
+    // 32-byte pieces by 128-bit loads through L1.
+    float4 cs[STAGED ? 1 : 2][STAGED ? 1 : NCH][2];
+    auto issue_cs_half = [&](int h, const int (&ps)[2]) {
+      if constexpr (STAGED) {
+        const int pos = j == 0 ? ps[0] : ps[1];
+        const bool mine = j < 2 && pos >= 0;
+        const uint32_t n_rows = __popc(__ballot_sync(0xffffffffu, mine));
+        const uint32_t bar = bar_cs + 8 * h;
+        if (lane == 0) mbar_expect_tx(bar, n_rows * (DH * 2));
+        __syncwarp();
+        if (mine) {
+          const int row = r + 8 * j;
+          bulk_copy_g2s(smem_u32(cs_warp) + h * CS_HALF + row * CS_PITCH,
+                        p.rope_table + (int64_t)clamp_pos(pos) * DH + h * (DH / 2), DH * 2, bar);
+        }
+      }
+    };
+    auto issue_cs_regs = [&](const int (&ps)[2]) {
+      if constexpr (ROT && !STAGED) {
+#pragma unroll
+        for (int tk = 0; tk < 2; ++tk) {
+          const float4* rp = reinterpret_cast<const float4*>(p.rope_table + (int64_t)clamp_pos(ps[tk]) * DH) + j * 2;
+#pragma unroll
+          for (int i = 0; i < NCH; ++i) {
+            cs[tk][i][0] = __ldg(rp + i * 8);
+            cs[tk][i][1] = __ldg(rp + i * 8 + 1);
           }
         }
       }
-      cp_async_commit();
     };
-
-    auto load_kwords = [&](int kk, KWords& w) {
-      w.th0 = w.th1 = w.rd0 = w.rd1 = w.rd2 = 0u;
-      w.th_sh = w.rd_sh = 0;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) w.sc[i] = 0.f;
-      if (kk >= nt || (kSkip & 16)) return;
-      const TileMeta m = get_meta(kk);
-      if (m.phys < 0) return;
-      const uint32_t tw = tier_of(meta_slot(m));
-      if (((tw >> 8) & 0xF) == 1)
-        load_kwords_t<DH, 1>(p, m, tile_sub(kk), tw & 0xFF, ut, uhalf, w);
-      else
-        load_kwords_t<DH, 2>(p, m, tile_sub(kk), tw & 0xFF, ut, uhalf, w);
-    };
-    // key positions of rows r and r+8 of tile kk (-1: no token)
-    auto load_pos = [&](int kk, int (&ps)[2]) {
-      ps[0] = ps[1] = -1;
-      if (!ROT || kk >= nt) return;
-      const TileMeta m = get_meta(kk);
-      if (m.phys < 0) return;
-      const int32_t* pp = p.positions + (int64_t)m.phys * N + 16 * tile_sub(kk);
-      ps[0] = pp[r];
-      ps[1] = pp[r + 8];
-    };
-
-    float4 cs[2][HS][2];
-    auto issue_cs = [&](const int (&ps)[2]) {
-      if constexpr (ROT && !(kSkip & 32)) {
-#pragma unroll
-      for (int tk = 0; tk < 2; ++tk) {
-        int pos = ps[tk];
-        if (pos >= p.max_pos) {
-          if (p.status) atomicOr(p.status, SPHKV_ST_BAD_POSITION);
-          pos = 0;
-        }
-        if (pos < 0) pos = 0;
-        const float4* rp = reinterpret_cast<const float4*>(p.rope_table + (int64_t)pos * DH) + j * 2;
-#pragma unroll
-        for (int s = 0; s < HS; ++s) {
-          // through L1 on purpose: a lane's cos and sin vectors share a 32-byte sector (and one
-          // 256-bit load for both measured slower than the two 128-bit ones)
-          cs[tk][s][0] = __ldg(rp + s * 8);
-          cs[tk][s][1] = __ldg(rp + s * 8 + 1);
-        }
+    auto wait_cs_half = [&](int h) -> bool {
+      bool ok = true;
+      if constexpr (STAGED) {
+        ok = mbar_wait(bar_cs + 8 * h, cs_waited[h] & 1u);
+        ++cs_waited[h];
       }
-      }
+      return ok;
     };
 
     auto stage_codebooks = [&]() {
       if (hkv == cb_head_loaded) return;
       const sphkv_tiers& tg = p.tiers;
       for (int s = 0; s < tg.n_slots; ++s) {
-        // one thread per 16-dim sub-row: four 128-bit loads, four 128-bit stores in the
-        // lane-quad order (2j, 2j+1, 2j+8, 2j+9)
-        const int g = tg.g[s], bits = tg.bits[s], G = DH / g, spg = g >> 4;
-        const float* src =
-            p.codebooks + ((int64_t)(hkv * tg.n_slots + s) * tg.G_max) * tg.C_max * tg.g_max;
+        // natural order [group][centroid][g floats]; a duplicated slot (g = 16) keeps two
+        // copies of every 64-byte row in one 128-byte slot, the second for odd token rows
+        const int g = tg.g[s], bits = tg.bits[s], G = DH / g, cpr = g >> 2;
+        const int dup = a.cb_dup[s];
+        const float* src = p.codebooks + ((int64_t)(hkv * tg.n_slots + s) * tg.G_max) * tg.C_max * tg.g_max;
         float4* dst = reinterpret_cast<float4*>(cb_smem + a.cb_smem_off[s]);
-        const int rows = (G << bits) * spg;
-#pragma unroll 2
-        for (int row = threadIdx.x; row < rows; row += blockDim.x) {
-          const int sub2 = row & (spg - 1), gc = row / spg;
-          const int c = gc & ((1 << bits) - 1), gam = gc >> bits;
-          const float4* sp = reinterpret_cast<const float4*>(
-              src + ((int64_t)gam * tg.C_max + c) * tg.g_max + sub2 * 16);
-          const float4 v0 = __ldg(sp), v1 = __ldg(sp + 1), v2 = __ldg(sp + 2), v3 = __ldg(sp + 3);
-          // each 64-byte sub-row is stored twice, at bytes 0 and 64 of a 128-byte slot: even
-          // tokens read the first copy, odd tokens the second, so the two tokens served by one
-          // shared-memory wavefront never meet in a bank
-          const float4 w0 = make_float4(v0.x, v0.y, v2.x, v2.y), w1 = make_float4(v0.z, v0.w, v2.z, v2.w);
-          const float4 w2 = make_float4(v1.x, v1.y, v3.x, v3.y), w3 = make_float4(v1.z, v1.w, v3.z, v3.w);
-          constexpr int SL = kCbPitch / 16;
-          dst[row * SL + 0] = w0; dst[row * SL + 1] = w1; dst[row * SL + 2] = w2; dst[row * SL + 3] = w3;
-          if (SPHKV_CB_DUP) {
-            dst[row * SL + 4] = w0; dst[row * SL + 5] = w1; dst[row * SL + 6] = w2; dst[row * SL + 7] = w3;
+        const int chunks = (G << bits) * cpr;
+        for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
+          const int c4 = i % cpr, row = i / cpr;
+          const int c = row & ((1 << bits) - 1), gam = row >> bits;
+          const float4 v = __ldg(reinterpret_cast<const float4*>(src + ((int64_t)gam * tg.C_max + c) * tg.g_max) + c4);
+          if (dup) {
+            dst[row * 8 + c4] = v;
+            dst[row * 8 + 4 + c4] = v;
+          } else {
+            dst[i] = v;
           }
         }
       }
       cb_head_loaded = hkv;
     };
 
-    // query fragments, B operand [k = dim][n = head], fp16 hi/lo, pre-scaled by
-    // sm_scale * log2(e); one copy per CTA in shared memory: q_smem[hl][step][lane]
-    auto stage_q = [&]() {
-      for (int i = threadIdx.x; i < KS * 32; i += blockDim.x) {
-        const int s = i >> 5, ln = i & 31, n = ln >> 2, jj = ln & 3;
-        const int head = PACK ? (n & 3) : n;
-        const bool real = head < a.grp;
-        const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + head) * DH;
-        float v[4];
+    // query fragments (B operand [k = dim][n = column]) in registers, pre-scaled by
+    // sm_scale * log2(e).  Column n of a packed tile: head n & 3, hi part for n < 4, lo part
+    // otherwise; unpacked: qh = hi parts, ql = lo parts of head n.
+    uint32_t qh[2 * NCH][QR], ql[PACK ? 1 : 2 * NCH][PACK ? 1 : QR];
+    auto load_q = [&]() {
+      const int n = r;  // B-fragment column of this lane
+      const int head = PACK ? (n & 3) : n;
+      const bool real = head < a.grp;
+      const int64_t qbase = ((int64_t)b * p.Hq + (int64_t)hkv * a.grp + head) * DH;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int d = 16 * s + 2 * jj + (e & 1) + ((e >> 1) << 3);
-          v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
+      for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+        for (int i = 0; i < NCH; ++i) {
+          float v[4], hi[4], lo[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int d = hf * (DH / 2) + lane_freq(DH, i, j, e);
+            v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
+            const uint32_t msk = kSplit == 2 ? 0xFFFFE000u : 0xFFFF0000u;
+            hi[e] = __uint_as_float(__float_as_uint(v[e]) & msk);
+            lo[e] = v[e] - hi[e];
+          }
+          const int s = hf * NCH + i;
+          if (kSplit == 2) {
+            // k8 step t: b0 = value 2t (k = j), b1 = value 2t + 1 (k = j + 4)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (PACK) {
+                qh[s][e] = __float_as_uint(n < 4 ? hi[e] : lo[e]);
+              } else {
+                qh[s][e] = __float_as_uint(hi[e]);
+                ql[PACK ? 0 : s][PACK ? 0 : e] = __float_as_uint(lo[e]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e2 = 0; e2 < 2; ++e2) {
+              const uint32_t h2 = __byte_perm(__float_as_uint(hi[2 * e2]), __float_as_uint(hi[2 * e2 + 1]), 0x7632);
+              __nv_bfloat162 lb = __floats2bfloat162_rn(lo[2 * e2], lo[2 * e2 + 1]);
+              const uint32_t l2 = *reinterpret_cast<uint32_t*>(&lb);
+              if (PACK) {
+                qh[s][e2] = n < 4 ? h2 : l2;
+              } else {
+                qh[s][e2] = h2;
+                ql[PACK ? 0 : s][PACK ? 0 : e2] = l2;
+              }
+            }
+          }
         }
-        uint2 hi, lo;
-        split_pair(f2(v[0], v[1]), hi.x, lo.x);
-        split_pair(f2(v[2], v[3]), hi.y, lo.y);
-        if (PACK) {
-          q_smem[i] = n < 4 ? hi : lo;   // columns 0..3: hi halves, 4..7: lo halves
-        } else {
-          q_smem[i] = hi;
-          q_smem[KS * 32 + i] = lo;
-        }
-      }
     };
 
     // online-softmax state: this lane's two head columns (2j, 2j+1)
@@ -578,23 +658,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
     // ---- prologue: the block-table -> pointer-table -> header chain of the first 16 tiles
     //      is interleaved with the codebook and query loads so their latencies overlap ----
-    __syncthreads();  // the previous segment is done with shared memory
+    fence_async_smem();  // this thread's plain shared-memory writes before the next async copies
+    __syncthreads();     // the previous segment is done with shared memory
     meta_stage0(0);
     stage_codebooks();
     meta_stage1();
-    stage_q();
+    load_q();
     meta_stage2(0);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < kVStages - 1; ++i) issue_v(i);
-    KWords cur, nx;
-    int pos_c[2], pos_1[2], pos_2[2];  // positions of tiles k, k+1, k+2
-    load_kwords(0, cur);
-    load_pos(0, pos_c);
-    load_pos(1, pos_1);
-    issue_cs(pos_c);
+    KRaw kw_a, kw_b, kw_c;  // page words of tiles k, k+1, k+2 (rotating)
+    load_kraw(0, kw_a);
+    load_kraw(1, kw_b);
+    if (nt > 0) {
+      issue_cs_half(0, kw_a.pos);
+      issue_cs_half(1, kw_a.pos);
+      issue_cs_regs(kw_a.pos);
+    }
 
-    for (int k = 0; k < nt; ++k) {
+    // one tile: `cur` holds tile k, `nx1` tile k + 1 (its positions start the next cos/sin
+    // copies), `nx2` receives the loads of tile k + 2.  Returns false when a wait gave up.
+    auto tile_step = [&](const int k, KRaw& cur, KRaw& nx1, KRaw& nx2) -> bool {
       {  // fetch the next 16 tiles' metadata into the idle half of the ring, in three steps
         const int ph = k & 15, kb = (k & ~15) + 16;
         if (ph == 0) meta_stage0(kb);
@@ -602,65 +687,152 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
         else if (ph == 10) { meta_stage2(kb); __syncwarp(); }
       }
       issue_v(k + kVStages - 1);  // into the stage tile k - 1 has just released
-      load_kwords(k + 1, nx);
-      load_pos(k + 2, pos_2);
+      load_kraw(k + 2, nx2);
       const TileMeta m = get_meta(k);
       const int sub = tile_sub(k);
       const int cnt_tile = m.phys < 0 ? 0 : min(16, max(0, meta_count(m) - 16 * sub));
+      const bool live = cnt_tile > 0;
+      bool ok_wait = true;
 
-      if (cnt_tile > 0) {
-        // ---- phase A: unpack codes/radii of (token ut, half uhalf) ------------------
-        if constexpr (!(kSkip & 1)) {
-          const uint32_t tw = tier_of(meta_slot(m));
-          const uint32_t cbase = tw >> 12;
-          if (((tw >> 8) & 0xF) == 1)
-            unpack_t<DH, 1>(cur, m, sub, tw & 0xFF, fmt, cbase, ut, uhalf, unp);
-          else
-            unpack_t<DH, 2>(cur, m, sub, tw & 0xFF, fmt, cbase, ut, uhalf, unp);
-        }
-        __syncwarp();
-
-        // ---- phase B: rebuild rotated key tile in A fragments, QK^T on tensor cores -
-        float s_hh[4] = {0.f, 0.f, 0.f, 0.f}, s_lh[4] = {0.f, 0.f, 0.f, 0.f},
-              s_hl[4] = {0.f, 0.f, 0.f, 0.f};
+      // ---- this lane's centroid rows and radii for tokens r, r + 8 ------------------------
+      uint32_t row_lo[2] = {cb_u32, cb_u32}, row_hi[2] = {cb_u32, cb_u32};
+      float rad_lo[2] = {0.f, 0.f}, rad_hi[2] = {0.f, 0.f};
+      if (live) {
+        const uint32_t tw = tier_of(meta_slot(m));
+        const int bits = tw & 0xFF;
+        const uint32_t cmask = (1u << bits) - 1u;
+        const int dup = (tw >> 12) & 1;
+        const int row_shift = (int)((tw >> 8) & 0xF) + 2 + dup;
+        int G, glo, ghi, sub_off;
+        lane_groups(tw, G, glo, ghi, sub_off);
+        const uint32_t base = cb_u32 + (tw >> 13) + sub_off * 4 + (dup ? (r & 1) * 64 : 0);
+        const int roff = meta_roff(m);
 #pragma unroll
-        for (int s = 0; s < ((kSkip & 2) ? 0 : HS); ++s) {
-          uint32_t a_lo_hi[4], a_lo_lo[4], a_hi_hi[4], a_hi_lo[4];
+        for (int tk = 0; tk < 2; ++tk) {
+          const int tp = 16 * sub + r + 8 * tk;
+          const bool tok_ok = tp < meta_count(m);
 #pragma unroll
-          for (int tk = 0; tk < 2; ++tk) {
-            const int tau = r + 8 * tk;
-            const uint2 e0 = unp[tau * KS + s];
-            const uint2 e1 = unp[tau * KS + s + HS];
-            const float4 x = *reinterpret_cast<const float4*>(cb_lane + e0.x);
-            const float4 y = *reinterpret_cast<const float4*>(cb_lane + e1.x);
-            build_pair<ROT>(x, y, __uint_as_float(e0.y), __uint_as_float(e1.y), cs[tk][s][0],
-                            cs[tk][s][1], tk, a_lo_hi, a_lo_lo, a_hi_hi, a_hi_lo);
+          for (int hf = 0; hf < 2; ++hf) {
+            const int grp = hf ? ghi : glo;
+            const int idx = tp * G + grp;
+            const int bit = idx * bits;
+            const int ba = m.toff + (bit >> 3);
+            const uint32_t code =
+                __funnelshift_r(cur.tw0[2 * tk + hf], cur.tw1[2 * tk + hf], (ba & 3) * 8 + (bit & 7)) & cmask;
+            const uint32_t row = base + ((((uint32_t)grp << bits) + code) << row_shift);
+            const int ra = roff + idx * rb;
+            float rad;
+            if (fmt == SPHKV_RADIUS_F16) {
+              const uint32_t hv = __funnelshift_r(cur.rw0[2 * tk + hf], cur.rw1[2 * tk + hf], (ra & 3) * 8);
+              rad = __half2float(__ushort_as_half((unsigned short)(hv & 0xFFFFu)));
+            } else {
+              const int c8 = (int)(int8_t)((cur.rw0[2 * tk + hf] >> ((ra & 3) * 8)) & 0xFFu);
+              rad = (cur.sc[hf] * (float)c8) * (1.0f / 127.0f);
+            }
+            if (!tok_ok) rad = 0.f;
+            if (hf) { row_hi[tk] = row; rad_hi[tk] = rad; } else { row_lo[tk] = row; rad_lo[tk] = rad; }
           }
-          if (PACK) {
-            const uint2 q0 = q_smem[s * 32 + lane], q1 = q_smem[(s + HS) * 32 + lane];
-            SPHKV_QK_MMA(s_hh, a_lo_hi, q0.x, q0.y);
-            SPHKV_QK_MMA(s_lh, a_lo_lo, q0.x, q0.y);
-            SPHKV_QK_MMA(s_hh, a_hi_hi, q1.x, q1.y);
-            SPHKV_QK_MMA(s_lh, a_hi_lo, q1.x, q1.y);
+        }
+      }
+
+      // ---- rebuild the rotated key tile chunk by chunk, QK^T on tensor cores ---------------
+      float s_h[4] = {0.f, 0.f, 0.f, 0.f}, s_l[4] = {0.f, 0.f, 0.f, 0.f}, s_x[4] = {0.f, 0.f, 0.f, 0.f};
+      auto qk_chunk = [&](int s, const float2 (&v)[2][2]) {
+        // v[token][pair]: the four values of chunk s for rows r and r + 8
+        if constexpr (kSplit == 2) {
+          uint32_t ah[2][4], al[2][4];
+#pragma unroll
+          for (int tk = 0; tk < 2; ++tk)
+#pragma unroll
+            for (int e2 = 0; e2 < 2; ++e2) {
+              const uint32_t x0 = __float_as_uint(v[tk][e2].x), x1 = __float_as_uint(v[tk][e2].y);
+              const uint32_t h0 = x0 & 0xFFFFE000u, h1 = x1 & 0xFFFFE000u;
+              const float2 l = __ffma2_rn(f2(__uint_as_float(h0), __uint_as_float(h1)), f2(-1.f, -1.f), v[tk][e2]);
+              ah[tk][2 * e2] = h0; ah[tk][2 * e2 + 1] = h1;
+              al[tk][2 * e2] = __float_as_uint(l.x); al[tk][2 * e2 + 1] = __float_as_uint(l.y);
+            }
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const uint32_t b0 = qh[s][2 * t], b1 = qh[s][2 * t + 1];
+            mma_tf32_1688(s_h, ah[0][2 * t], ah[1][2 * t], ah[0][2 * t + 1], ah[1][2 * t + 1], b0, b1);
+            mma_tf32_1688(s_l, al[0][2 * t], al[1][2 * t], al[0][2 * t + 1], al[1][2 * t + 1], b0, b1);
+            if (!PACK)
+              mma_tf32_1688(s_x, ah[0][2 * t], ah[1][2 * t], ah[0][2 * t + 1], ah[1][2 * t + 1],
+                            ql[PACK ? 0 : s][PACK ? 0 : 2 * t], ql[PACK ? 0 : s][PACK ? 0 : 2 * t + 1]);
+          }
+        } else {
+          uint32_t ah[4], al[4];
+#pragma unroll
+          for (int tk = 0; tk < 2; ++tk)
+#pragma unroll
+            for (int e2 = 0; e2 < 2; ++e2) {
+              const uint32_t x0 = __float_as_uint(v[tk][e2].x), x1 = __float_as_uint(v[tk][e2].y);
+              const uint32_t h0 = x0 & 0xFFFF0000u, h1 = x1 & 0xFFFF0000u;
+              const float2 l = __ffma2_rn(f2(__uint_as_float(h0), __uint_as_float(h1)), f2(-1.f, -1.f), v[tk][e2]);
+              ah[tk + 2 * e2] = __byte_perm(x0, x1, 0x7632);
+              al[tk + 2 * e2] = __byte_perm(__float_as_uint(l.x), __float_as_uint(l.y), 0x7632);
+            }
+          mma_bf16_16816(s_h, ah, qh[s][0], qh[s][1]);
+          mma_bf16_16816(s_l, al, qh[s][0], qh[s][1]);
+          if (!PACK) mma_bf16_16816(s_x, ah, ql[PACK ? 0 : s][0], ql[PACK ? 0 : s][PACK ? 0 : 1]);
+        }
+      };
+      auto do_chunk = [&](int i) {
+        float2 lo[2][2], hi[2][2];
+#pragma unroll
+        for (int tk = 0; tk < 2; ++tk) {
+          const float4 x = lds128(row_lo[tk] + coff[i]);
+          const float4 y = lds128(row_hi[tk] + coff[i]);
+          const float2 rl = f2(rad_lo[tk], rad_lo[tk]), rh = f2(rad_hi[tk], rad_hi[tk]);
+          const float2 x0 = __fmul2_rn(f2(x.x, x.y), rl), x1 = __fmul2_rn(f2(x.z, x.w), rl);
+          const float2 y0 = __fmul2_rn(f2(y.x, y.y), rh), y1 = __fmul2_rn(f2(y.z, y.w), rh);
+          if constexpr (ROT) {
+            float4 c, sn;
+            if constexpr (STAGED) {
+              const uint32_t ad = cs_lane + tk * 8 * CS_PITCH + (i / NH) * CS_HALF + (i % NH) * 128;
+              c = lds128(ad);
+              sn = lds128(ad + 16);
+            } else {
+              c = cs[STAGED ? 0 : tk][STAGED ? 0 : i][0];
+              sn = cs[STAGED ? 0 : tk][STAGED ? 0 : i][1];
+            }
+            const float2 c0 = f2(c.x, c.y), c1 = f2(c.z, c.w);
+            const float2 s0 = f2(sn.x, sn.y), s1 = f2(sn.z, sn.w);
+            const float2 n0 = f2(-sn.x, -sn.y), n1 = f2(-sn.z, -sn.w);
+            lo[tk][0] = __ffma2_rn(y0, n0, __fmul2_rn(x0, c0));
+            lo[tk][1] = __ffma2_rn(y1, n1, __fmul2_rn(x1, c1));
+            hi[tk][0] = __ffma2_rn(x0, s0, __fmul2_rn(y0, c0));
+            hi[tk][1] = __ffma2_rn(x1, s1, __fmul2_rn(y1, c1));
           } else {
-            const uint2 qh0 = q_smem[s * 32 + lane], ql0 = q_smem[(KS + s) * 32 + lane];
-            const uint2 qh1 = q_smem[(s + HS) * 32 + lane], ql1 = q_smem[(KS + s + HS) * 32 + lane];
-            SPHKV_QK_MMA(s_hh, a_lo_hi, qh0.x, qh0.y);
-            SPHKV_QK_MMA(s_lh, a_lo_lo, qh0.x, qh0.y);
-            SPHKV_QK_MMA(s_hl, a_lo_hi, ql0.x, ql0.y);
-            SPHKV_QK_MMA(s_hh, a_hi_hi, qh1.x, qh1.y);
-            SPHKV_QK_MMA(s_lh, a_hi_lo, qh1.x, qh1.y);
-            SPHKV_QK_MMA(s_hl, a_hi_hi, ql1.x, ql1.y);
+            lo[tk][0] = x0; lo[tk][1] = x1; hi[tk][0] = y0; hi[tk][1] = y1;
           }
         }
-        // the cos/sin registers are free now: fetch the next tile's rows
-        issue_cs(pos_1);
+        qk_chunk(i, lo);
+        qk_chunk(NCH + i, hi);
+      };
 
+      ok_wait &= wait_cs_half(0);
+      if (live) {
+#pragma unroll
+        for (int i = 0; i < NH; ++i) do_chunk(i);
+      }
+      __syncwarp();
+      if (k + 1 < nt) issue_cs_half(0, nx1.pos);
+      ok_wait &= wait_cs_half(1);
+      if (live) {
+#pragma unroll
+        for (int i = NH; i < NCH; ++i) do_chunk(i);
+      }
+      __syncwarp();
+      if (k + 1 < nt) { issue_cs_half(1, nx1.pos); issue_cs_regs(nx1.pos); }
+
+      float pv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (live) {
         // ---- online softmax over the 16 token rows, per head column ------------------
         float sv[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          sv[e] = s_hh[e] + (s_lh[e] + s_hl[e]);
+          sv[e] = s_h[e] + (s_l[e] + s_x[e]);
           // packed columns: head h's logit = column h (x q_hi) + column 4+h (x q_lo)
           if (PACK) sv[e] += __shfl_xor_sync(0xffffffffu, sv[e], 2);
         }
@@ -674,8 +846,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
                            16 * sub + tok] = sv[e] * kLn2;
           }
         }
-        const bool ok0 = r < cnt_tile && (!ROT || pos_c[0] >= 0);
-        const bool ok1 = (r + 8) < cnt_tile && (!ROT || pos_c[1] >= 0);
+        const bool ok0 = r < cnt_tile && (!ROT || cur.pos[0] >= 0);
+        const bool ok1 = (r + 8) < cnt_tile && (!ROT || cur.pos[1] >= 0);
         if (!ok0) sv[0] = sv[1] = -INFINITY;
         if (!ok1) sv[2] = sv[3] = -INFINITY;
         float tmax[2] = {fmaxf(sv[0], sv[2]), fmaxf(sv[1], sv[3])};
@@ -692,7 +864,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           alpha[c] = fast_exp2(m_run[c] - msafe[c]);
           m_run[c] = mn;
         }
-        float pv[4];
         pv[0] = fast_exp2(sv[0] - msafe[0]);
         pv[1] = fast_exp2(sv[1] - msafe[1]);
         pv[2] = fast_exp2(sv[2] - msafe[0]);
@@ -730,74 +901,77 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
 
         // ---- P^T through shared memory into the B-operand layout -------------------
         // pbuf[h][head][token]: fp16 (or bf16 hi / lo for a bf16 V pool)
-        {
-          uint16_t* ph = pbuf;
-          uint16_t* pl = pbuf + 8 * 16;
+        uint16_t* ph = pbuf;
+        uint16_t* pl = pbuf + 8 * 16;
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int head = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
-            uint16_t hbits, lbits;
-            if (kBf16) {
-              const __nv_bfloat16 h = __float2bfloat16_rn(pv[e]);
-              hbits = __bfloat16_as_ushort(h);
-              lbits = __bfloat16_as_ushort(__float2bfloat16_rn(pv[e] - __bfloat162float(h)));
-            } else {
-              hbits = __half_as_ushort(__float2half_rn(pv[e]));
-              lbits = 0;
-            }
-            if (PACK) {
-              // columns 0..3 hold P (hi half), columns 4..7 the lo half (zero for an fp16 V pool)
-              ph[head * 16 + tok] = j < 2 ? hbits : lbits;
-            } else {
-              ph[head * 16 + tok] = hbits;
-              if (kBf16) pl[head * 16 + tok] = lbits;
-            }
+        for (int e = 0; e < 4; ++e) {
+          const int head = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
+          uint16_t hbits, lbits;
+          if (kBf16) {
+            const __nv_bfloat16 h = __float2bfloat16_rn(pv[e]);
+            hbits = __bfloat16_as_ushort(h);
+            lbits = __bfloat16_as_ushort(__float2bfloat16_rn(pv[e] - __bfloat162float(h)));
+          } else {
+            hbits = __half_as_ushort(__float2half_rn(pv[e]));
+            lbits = 0;
+          }
+          if (PACK) {
+            // columns 0..3 hold P (hi half), columns 4..7 the lo half (zero for an fp16 V pool)
+            ph[head * 16 + tok] = j < 2 ? hbits : lbits;
+          } else {
+            ph[head * 16 + tok] = hbits;
+            if (kBf16) pl[head * 16 + tok] = lbits;
           }
         }
-        cp_async_wait<kVStages - 1>();  // tile k's copy has landed (later ones may be in flight)
-        __syncwarp();
-        {
-          const uint32_t* ph32 = reinterpret_cast<const uint32_t*>(pbuf);
-          const uint32_t b0 = ph32[(r * 16 + 2 * j) >> 1];
-          const uint32_t b1 = ph32[(r * 16 + 2 * j + 8) >> 1];
-          uint32_t c0 = 0, c1 = 0;
-          if (kBf16 && !PACK) {
-            c0 = ph32[(8 * 16 + r * 16 + 2 * j) >> 1];
-            c1 = ph32[(8 * 16 + r * 16 + 2 * j + 8) >> 1];
-          }
-          // ---- acc^T[dh][head] += V^T[dh][token] P^T[token][head] ---------------------
-          const uint32_t vbase = smem_u32(v_ring + (k % kVStages) * V_TILE);
-          const int mi = lane >> 3;
-          const int tau = (lane & 7) + ((mi >> 1) << 3);
-#pragma unroll
-          for (int dt = 0; dt < ((kSkip & 4) ? 0 : KS); ++dt) {
-            const int c = 2 * dt + (mi & 1);
-            uint32_t af[4];
-            ldmatrix_x4_trans(af, vbase + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4));
-            if (kBf16) {
-              mma_bf16_16816(acc[dt], af, b0, b1);
-              if (!PACK) mma_bf16_16816(acc[dt], af, c0, c1);
-            } else {
-              mma_f16_16816(acc[dt], af, b0, b1);
-            }
-          }
+      } else if (EXTRA && ml_seg != nullptr && lane < a.grp) {  // a tile without tokens: (-inf, 0)
+        float* dst = ml_seg + lane * ml_head + 2 * kWarps * k;
+        dst[0] = -INFINITY;
+        dst[1] = 0.f;
+      }
+      uint32_t v_stage;
+      ok_wait &= wait_v(v_stage);  // tile k's V has landed
+      __syncwarp();
+      if (live) {
+        const uint32_t* ph32 = reinterpret_cast<const uint32_t*>(pbuf);
+        const uint32_t b0 = ph32[(r * 16 + 2 * j) >> 1];
+        const uint32_t b1 = ph32[(r * 16 + 2 * j + 8) >> 1];
+        uint32_t c0 = 0, c1 = 0;
+        if (kBf16 && !PACK) {
+          c0 = ph32[(8 * 16 + r * 16 + 2 * j) >> 1];
+          c1 = ph32[(8 * 16 + r * 16 + 2 * j + 8) >> 1];
         }
-        __syncwarp();
-      } else {
-        issue_cs(pos_1);
-        cp_async_wait<kVStages - 1>();
-        __syncwarp();
-        if (EXTRA && ml_seg != nullptr && lane < a.grp) {  // a tile without tokens: (-inf, 0)
-          float* dst = ml_seg + lane * ml_head + 2 * kWarps * k;
-          dst[0] = -INFINITY;
-          dst[1] = 0.f;
+        // ---- acc^T[dh][head] += V^T[dh][token] P^T[token][head] ---------------------
+        const uint32_t vbase = smem_u32(v_ring) + v_stage * V_TILE;
+        const int mi = lane >> 3;
+        const int tau = (lane & 7) + ((mi >> 1) << 3);
+#pragma unroll
+        for (int dt = 0; dt < KS; ++dt) {
+          const int c = 2 * dt + (mi & 1);
+          uint32_t af[4];
+          ldmatrix_x4_trans(af, vbase + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4));
+          if (kBf16) {
+            mma_bf16_16816(acc[dt], af, b0, b1);
+            if (!PACK) mma_bf16_16816(acc[dt], af, c0, c1);
+          } else {
+            mma_f16_16816(acc[dt], af, b0, b1);
+          }
         }
       }
-      cur = nx;
-      pos_c[0] = pos_1[0]; pos_c[1] = pos_1[1];
-      pos_1[0] = pos_2[0]; pos_1[1] = pos_2[1];
+      __syncwarp();
+      if (!__all_sync(0xffffffffu, ok_wait)) {
+        // an async copy never completed: flag it and stop; the partial row of this segment is
+        // not meaningful and the host sees the status bit
+        if (lane == 0 && p.status) atomicOr(p.status, SPHKV_ST_TIMEOUT);
+        dead = true;
+        return false;
+      }
+      return true;
+    };
+    for (int k = 0; k < nt; k += 3) {
+      if (!tile_step(k, kw_a, kw_b, kw_c)) break;
+      if (k + 1 < nt && !tile_step(k + 1, kw_b, kw_c, kw_a)) break;
+      if (k + 2 < nt && !tile_step(k + 2, kw_c, kw_a, kw_b)) break;
     }
-    cp_async_wait<0>();
 
     // ---- merge the warps of this CTA and write one partial row ---------------------
 #pragma unroll
@@ -806,7 +980,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
       l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], o);
     }
     __syncthreads();  // every warp is done with its V ring
-    {
+    if (!dead) {
       float* wbuf = reinterpret_cast<float*>(v_ring);  // [8 heads][DH + 2]
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -821,6 +995,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const Dec
           wbuf[n * (DH + 2) + 2 + 16 * dt + r + 8] = acc[dt][2 + c];
         }
       }
+    } else if (lane < 8) {
+      reinterpret_cast<float*>(v_ring)[lane * (DH + 2)] = -INFINITY;  // contributes nothing
     }
     __syncthreads();
     {
@@ -1018,11 +1194,20 @@ __global__ void merge_partials_kernel(const float* __restrict__ parts, int R, in
 // ---- host side --------------------------------------------------------------------------------
 static int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
-static int smem_cb_layout(const sphkv_tiers& t, int dh, int* offs) {
+// Shared-memory layout of the codebooks: a g = 16 slot may be stored twice (row pitch 128
+// bytes, second copy for odd token rows) when the policy asks for it and the space is there.
+static int smem_cb_layout(const sphkv_tiers& t, int dh, int budget_bytes, int* offs, int* dup) {
+  int plain = 0;
+  for (int s = 0; s < t.n_slots; ++s) plain += dh * (1 << t.bits[s]) * 4;
+  int extra_left = budget_bytes - plain;
   int off = 0;
   for (int s = 0; s < t.n_slots; ++s) {
+    const int bytes = dh * (1 << t.bits[s]) * 4;
+    const bool want = t.g[s] == 16 && (SPHKV_CB_DUP == 2 || (SPHKV_CB_DUP == 1 && t.bits[s] <= 4));
+    dup[s] = (want && bytes <= extra_left) ? 1 : 0;
+    if (dup[s]) extra_left -= bytes;
     offs[s] = off;
-    off += dh * (1 << t.bits[s]) * 4 * (kCbPitch / 64);
+    off += bytes * (dup[s] ? 2 : 1);
   }
   return off;
 }
@@ -1044,27 +1229,48 @@ int validate_tiers(const sphkv_tiers& t, int dh) {
   return 0;
 }
 
+// ---- tensor map of the V pool ------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    tried = true;
+  }
+  return fn;
+}
+
+// V pool viewed as a 2-D tensor [n_pages * page_size rows][dh] of 16-bit elements; a box is 16
+// rows x 64 elements (128 bytes, the widest row the 128-byte swizzle takes).  Encoding is host
+// arithmetic only (no device memory, no driver state).
+static int make_v_map(CUtensorMap* map, const sphkv_decode_params& p) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  SPHKV_REQUIRE(fn != nullptr, SPHKV_E_ARG, "decode: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)p.dh, (cuuint64_t)p.n_pages * (cuuint64_t)p.page_size};
+  const cuuint64_t strides[1] = {(cuuint64_t)p.dh * 2};
+  const cuuint32_t box[2] = {64, 16};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, p.v_dtype == SPHKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                         2, const_cast<void*>(p.v_pool), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  SPHKV_REQUIRE(rc == CUDA_SUCCESS, SPHKV_E_ARG, "decode: cuTensorMapEncodeTiled failed (%d) for the V pool", (int)rc);
+  return 0;
+}
+
 template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
 static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
-  static int configured_for = -1;
+  static SmemOptIn opt_in;
   auto kern = decode_splitk_kernel<DH, VT, ROT, EXTRA, PACK>;
-  if (configured_for < smem_bytes) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) {
-      set_error("cudaFuncSetAttribute(decode, %d B): %s", smem_bytes, cudaGetErrorString(e));
-      return (int)e;
-    }
-    // Ask for the smallest shared-memory carve-out that holds this CTA (plus the 1 KB the system
-    // reserves): what is left of the 256 KB array is L1, which serves the cos/sin table rows.
-    // The hint is a percentage of 228 KB that the driver rounds UP to a supported size, so it is
-    // rounded down here (the driver never goes below what the launch needs).
-    cudaFuncAttributes fa;
-    const int64_t stat = cudaFuncGetAttributes(&fa, kern) == cudaSuccess ? (int64_t)fa.sharedSizeBytes : 0;
-    const int pct = (int)(((int64_t)smem_bytes + stat + 1024) * 100 / (228 * 1024));
-    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, pct > 100 ? 100 : pct);
-    configured_for = smem_bytes;
-  }
+  if (int rc = ensure_dynamic_smem(opt_in, (const void*)kern, smem_bytes, "decode")) return rc;
   kern<<<a.n_ctas, kWarps * 32, smem_bytes, st>>>(a);
   return check_launch("decode_splitk_kernel");
 }
@@ -1089,23 +1295,19 @@ static int launch_decode(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
 
 using namespace sphkv;
 
-extern "C" int sphkv_sm_count(void) {
-  int dev = 0, n = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  if (e != cudaSuccess) {
-    set_error("sm_count: %s", cudaGetErrorString(e));
-    return -(int)e;
-  }
-  return n;
+extern "C" int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh,
+                                      const float* inv_freq, void* stream) {
+  SPHKV_REQUIRE(table && inv_freq, SPHKV_E_ARG, "rope_table: NULL pointer");
+  SPHKV_REQUIRE(max_pos > 0 && (dh == 64 || dh == 128), SPHKV_E_ARG, "rope_table: max_pos=%d dh=%d",
+                max_pos, dh);
+  SPHKV_REQUIRE(((uintptr_t)table & 15) == 0, SPHKV_E_ALIGN, "rope_table: table needs 16 B");
+  const int64_t n = (int64_t)max_pos * (dh / 2);
+  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      table, max_pos, dh, inv_freq);
+  return check_launch("rope_table_kernel");
 }
 
-static int resolve_ctas(int n_ctas) {
-  if (n_ctas > 0) return n_ctas;
-  static int cached = 0;
-  if (cached <= 0) cached = sphkv_sm_count();
-  return cached;
-}
+static int resolve_ctas(int n_ctas) { return n_ctas > 0 ? n_ctas : sm_count_current_device(); }
 
 extern "C" int64_t sphkv_decode_scratch_bytes(int32_t B, int32_t Hkv, int32_t dh, int32_t n_ctas) {
   n_ctas = resolve_ctas(n_ctas);
@@ -1123,6 +1325,8 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   SPHKV_REQUIRE(p.out || p.out_partial, SPHKV_E_ARG, "decode: out and out_partial both NULL");
   SPHKV_REQUIRE(p.rope_table == nullptr || p.positions != nullptr, SPHKV_E_ARG,
                 "decode: rope_table given without positions");
+  SPHKV_REQUIRE(p.rope_table == nullptr || p.max_pos > 0, SPHKV_E_ARG,
+                "decode: rope_table given with max_pos=%d (rows of the table)", p.max_pos);
   SPHKV_REQUIRE(p.omega == nullptr || p.page_ml != nullptr, SPHKV_E_ARG,
                 "decode: omega needs page_ml (the per-tile statistics it is computed from)");
   SPHKV_REQUIRE(p.dh == 64 || p.dh == 128, SPHKV_E_ARG, "decode: dh=%d (64 or 128)", p.dh);
@@ -1160,13 +1364,14 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   a.pfx = reinterpret_cast<int32_t*>(p.scratch);
   a.rows = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.scratch) +
                                     align_up((int64_t)(a.n_units + 1) * 4, 256));
-  a.cb_smem_bytes = smem_cb_layout(p.tiers, p.dh, a.cb_smem_off);
   a.plan_in_kernel = a.n_units <= kMaxUnitsInKernelPlan ? 1 : 0;
-  const int smem_bytes = smem_v_bytes(p.dh) + a.cb_smem_bytes + smem_q_bytes(p.dh, a.grp <= 4) +
-                         kWarps * smem_priv_bytes(p.dh) +
-                         (a.plan_in_kernel ? (a.n_units + 1) * 4 : 0);
+  const int fixed_bytes = smem_v_bytes(p.dh) + (p.rope_table ? smem_cs_bytes(p.dh) : smem_cs_bytes(p.dh)) +
+                          kWarps * smem_priv_bytes() + (a.plan_in_kernel ? (a.n_units + 1) * 4 : 0);
+  a.cb_smem_bytes = smem_cb_layout(p.tiers, p.dh, 227 * 1024 - fixed_bytes, a.cb_smem_off, a.cb_dup);
+  const int smem_bytes = fixed_bytes + a.cb_smem_bytes;
   SPHKV_REQUIRE(smem_bytes <= 227 * 1024, SPHKV_E_LIMIT,
                 "decode: codebooks need %d B of shared memory (limit %d)", smem_bytes, 227 * 1024);
+  if (int rc = make_v_map(&a.v_map, p)) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   if (!a.plan_in_kernel) {
@@ -1200,7 +1405,6 @@ extern "C" int sphkv_merge_partials(const float* parts, int32_t R, int32_t n_row
       parts, R, n_rows, dh, out, out_dtype);
   return check_launch("merge_partials_kernel");
 }
-
 // ---- decode without any caller- or library-side allocation -------------------------------
 // Some hosts of this library cannot hand it scratch memory: an inference server that gave
 // its whole HBM budget to the KV pools at start-up has nothing left for cudaMalloc to

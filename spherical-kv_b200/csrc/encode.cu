@@ -563,44 +563,11 @@ __global__ void __launch_bounds__(kEncThreads, kCodeTok <= 2 ? 2 : 1) encode_cod
   }
 }
 
-// ---- RoPE table ------------------------------------------------------------------------------
-// row(pos)[(s*4 + j)*8 + e]     = cos(float(pos) * inv_freq[f]),
-// row(pos)[(s*4 + j)*8 + 4 + e] = sin(...),  f = 16 s + 2 j + (e & 1) + 8 (e >> 1).
-// The fp32 product is rounded first, as the HF rotary module does, then cos/sin are
-// evaluated in double and rounded to fp32.
-__global__ void rope_table_kernel(float* __restrict__ table, int max_pos, int dh,
-                                  const float* __restrict__ inv_freq) {
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int half = dh / 2;
-  if (i >= (int64_t)max_pos * half) return;
-  const int pos = (int)(i / half), q = (int)(i - (int64_t)pos * half);
-  const int e = q & 3, jj = (q >> 2) & 3, s = q >> 4;
-  const int f = 16 * s + 2 * jj + (e & 1) + ((e >> 1) << 3);
-  const float ang = __fmul_rn((float)pos, inv_freq[f]);
-  double sn, cs;
-  sincos((double)ang, &sn, &cs);
-  float* row = table + (int64_t)pos * dh + (s * 4 + jj) * 8;
-  row[e] = (float)cs;
-  row[4 + e] = (float)sn;
-}
-
 int validate_tiers(const sphkv_tiers& t, int dh);
 
 }  // namespace sphkv
 
 using namespace sphkv;
-
-extern "C" int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh,
-                                      const float* inv_freq, void* stream) {
-  SPHKV_REQUIRE(table && inv_freq, SPHKV_E_ARG, "rope_table: NULL pointer");
-  SPHKV_REQUIRE(max_pos > 0 && (dh == 64 || dh == 128), SPHKV_E_ARG, "rope_table: max_pos=%d dh=%d",
-                max_pos, dh);
-  SPHKV_REQUIRE(((uintptr_t)table & 15) == 0, SPHKV_E_ALIGN, "rope_table: table needs 16 B");
-  const int64_t n = (int64_t)max_pos * (dh / 2);
-  rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      table, max_pos, dh, inv_freq);
-  return check_launch("rope_table_kernel");
-}
 
 template <int GS>
 static int launch_encode(const EncodeArgs& a, bool split, bool from_codes, int smem_bytes, cudaStream_t st) {
@@ -667,35 +634,23 @@ static int encode_impl(const sphkv_encode_params* pp, void* stream, bool from_co
   EncodeArgs a;
   a.p = p;
   {  // long runs per CTA amortise the codebook staging, but only once every SM has several CTAs
-    static int sms = 0;
-    if (sms <= 0) {
-      int dev = 0;
-      if (cudaGetDevice(&dev) != cudaSuccess ||
-          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-        sms = 148;
-    }
+    int sms = sm_count_current_device();
+    if (sms <= 0) sms = 148;
     int bpc = p.n_bundles / (sms * 8);
     a.bundles_per_cta = bpc < 1 ? 1 : (bpc > kMaxBundlesPerCta ? kMaxBundlesPerCta : bpc);
   }
   const int64_t scratch_need = sphkv_encode_scratch_bytes(p.n_pages, p.page_size, p.dh);
   const bool split = p.scratch != nullptr && p.scratch_bytes >= scratch_need &&
                      ((uintptr_t)p.scratch & 15) == 0;
-  static int configured = 0;
-  if (configured < smem_bytes) {
-    cudaError_t e = cudaSuccess;
-    auto set = [&](const void* f) {
-      if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    };
-    set((const void*)encode_bundle_kernel<16, 0>); set((const void*)encode_bundle_kernel<16, 1>);
-    set((const void*)encode_bundle_kernel<16, 2>); set((const void*)encode_bundle_kernel<32, 0>);
-    set((const void*)encode_bundle_kernel<32, 1>); set((const void*)encode_bundle_kernel<32, 2>);
-    set((const void*)encode_bundle_kernel<16, 3>); set((const void*)encode_bundle_kernel<32, 3>);
-    if (e != cudaSuccess) {
-      set_error("encode: cudaFuncSetAttribute(%d B): %s", smem_bytes, cudaGetErrorString(e));
-      return (int)e;
-    }
-    configured = smem_bytes;
+  {
+    static SmemOptIn opt_in[8];
+    const void* kernels[8] = {
+        (const void*)encode_bundle_kernel<16, 0>, (const void*)encode_bundle_kernel<16, 1>,
+        (const void*)encode_bundle_kernel<16, 2>, (const void*)encode_bundle_kernel<16, 3>,
+        (const void*)encode_bundle_kernel<32, 0>, (const void*)encode_bundle_kernel<32, 1>,
+        (const void*)encode_bundle_kernel<32, 2>, (const void*)encode_bundle_kernel<32, 3>};
+    for (int i = 0; i < 8; ++i)
+      if (int rc = ensure_dynamic_smem(opt_in[i], kernels[i], smem_bytes, "encode")) return rc;
   }
   // One launch per group size present; each skips the bundles of the other size.
   bool any16 = false, any32 = false;
@@ -748,14 +703,9 @@ extern "C" int sphkv_encode_codes(const void* k_src, int32_t k_dtype, int64_t k_
   SPHKV_REQUIRE(any, SPHKV_E_ARG, "encode_codes: no output requested");
   const int smem_bytes = off * 4;
   SPHKV_REQUIRE(smem_bytes <= 200 * 1024, SPHKV_E_LIMIT, "encode_codes: codebooks need %d B of shared memory", smem_bytes);
-  static int configured = 0;
-  if (configured < smem_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(encode_codes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) {
-      set_error("encode_codes: cudaFuncSetAttribute(%d B): %s", smem_bytes, cudaGetErrorString(e));
-      return (int)e;
-    }
-    configured = smem_bytes;
+  {
+    static SmemOptIn opt_in;
+    if (int rc = ensure_dynamic_smem(opt_in, (const void*)encode_codes_kernel, smem_bytes, "encode_codes")) return rc;
   }
   const int per_cta = (kEncThreads / 32) / (dh >> 5) * 32 * kCodeTok;  // rows per CTA
   const dim3 grid((unsigned)((rows + per_cta - 1) / per_cta), (unsigned)Hkv);

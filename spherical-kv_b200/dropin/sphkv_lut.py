@@ -44,6 +44,23 @@ def _st() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+def _f32_ptr(t, name: str, numel: int) -> int:
+    """Device pointer of a step input.  The reference extension reads these with
+    data_ptr<float>() (decode_kernel.cu:100-105, 271), which raises on another dtype; the same
+    here, plus device, contiguity and size, because the kernels read `numel` packed floats."""
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name}: expected a tensor")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"{name}: expected dtype torch.float32, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name}: expected a contiguous tensor")
+    if t.numel() != numel:
+        raise RuntimeError(f"{name}: expected {numel} elements, got {t.numel()}")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name}: expected a CUDA tensor")
+    return t.data_ptr()
+
+
 def make_tier_idx_map(tiers) -> Dict[int, int]:
     """Rank of every compressed tier among the non-zero tier ids (sphkv_lut.py:7-15)."""
     out, rank = {}, 0
@@ -207,8 +224,11 @@ class LayerPool:
         attention over the pool.  Two library calls; page roll-over happens on the device."""
         if self._decode_cb_flat is None:
             raise RuntimeError("LayerPool: no tier-1 codebook for every KV head")
+        q_ptr = _f32_ptr(q_post, "q_post", self.num_q * self.dh)
+        k_ptr = _f32_ptr(k_post, "k_post", self.num_kv * self.dh)
+        v_ptr = _f32_ptr(v_new, "v_new", self.num_kv * self.dh)
         _lib.check(_L.sphkv_pool_append_step(
-            k_post.data_ptr(), v_new.data_ptr(), self._decode_cb_flat.data_ptr(),
+            k_ptr, v_ptr, self._decode_cb_flat.data_ptr(),
             self.theta_codes.data_ptr(), self.radius_codes.data_ptr(), self.r_scales.data_ptr(),
             self.v_pool.data_ptr(), self.block_table_gpu.data_ptr(), self.bits_table_gpu.data_ptr(),
             self.ctx_lens_gpu.data_ptr(), self._pids.data_ptr(), self._state.data_ptr(),
@@ -216,7 +236,7 @@ class LayerPool:
             self.page_size, self.num_kv, self.max_blocks, self.n_total, _st()), "sphkv_pool_append_step")
         self._uniform_ctx += 1  # host mirror only; the kernels never read it
         _lib.check(_L.sphkv_pool_decode(
-            q_post.data_ptr(), self.cb_flat.data_ptr(), self.tier_G_gpu.data_ptr(),
+            q_ptr, self.cb_flat.data_ptr(), self.tier_G_gpu.data_ptr(),
             self.tier_g_gpu.data_ptr(), self.theta_codes.data_ptr(), self.radius_codes.data_ptr(),
             self.r_scales.data_ptr(), self.v_pool.data_ptr(), self.block_table_gpu.data_ptr(),
             self.bits_table_gpu.data_ptr(), self.ctx_lens_gpu.data_ptr(), self._out_buf.data_ptr(),

@@ -186,6 +186,9 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     spherical_kv_pipeline.py:952-987, updated in place inside the merge kernel from the
     per-tile statistics of this step; `page_ml` (f32 [B, Hq, max_blocks, page_size/16, 2]) is
     allocated when omega is given without it.
+    The split-K scratch and the status word live in `cache` (grown when a later call needs
+    more): one cache must not be decoded on two streams at once.  The status word is not read
+    here (that would synchronise); `check_status(cache)` does it.
     """
     lib = _lib.load()
     L = cache.lists
@@ -196,7 +199,8 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     if omega is not None:
         assert omega.dtype == torch.float32 and omega.is_contiguous() and omega.numel() == B * L.Hkv * L.max_blocks
     assert B == L.B and dh == cache.dh
-    if cache.scratch is None:
+    need = lib.sphkv_decode_scratch_bytes(L.B, L.Hkv, cache.dh, n_ctas)
+    if cache.scratch is None or cache.scratch.numel() < need:
         cache.scratch = decode_scratch(cache, n_ctas)
     if cache.status is None:
         cache.status = torch.zeros(1, dtype=torch.int32, device=q.device)
@@ -223,6 +227,22 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     p.tiers = cache.tiers.to_c()
     _lib.check(lib.sphkv_decode_paged(C.byref(p), _stream()), "sphkv_decode_paged")
     return out
+
+
+def check_status(cache: PagedCache) -> None:
+    """Host read of the cache's status word (synchronises); raises if a decode since the last
+    check met a bad block-table entry, tier slot or key position, or gave up on a copy."""
+    if cache.status is None:
+        return
+    st = int(cache.status.item())
+    if st:
+        names = [n for bit, n in ((_lib.ST_BAD_POSITION, "key position outside the RoPE table"),
+                                  (_lib.ST_BAD_BLOCK, "block-table entry >= n_pages"),
+                                  (_lib.ST_BAD_SLOT, "bits-table entry outside the tier slots"),
+                                  (_lib.ST_TIMEOUT, "an asynchronous copy did not complete"),
+                                  (_lib.ST_INTERNAL, "misaligned shared memory")) if st & bit]
+        cache.status.zero_()
+        raise _lib.SphKVError("decode status %d: %s" % (st, "; ".join(names)))
 
 
 def merge_partials(parts: torch.Tensor, out_dtype: torch.dtype = torch.float32,

@@ -4,7 +4,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import load_oracle, load_pkg
+from util import load_oracle, load_pkg, radius_code_mismatches_are_boundary_cases
 
 pkg = load_pkg()
 orc = load_oracle()
@@ -134,8 +134,12 @@ def test_encode_matches_reference_golden_pages():
                 th_g = orc.unpack_bits(got[t_rel:r_rel], n * G, tier.b_theta)
                 th_r = orc.unpack_bits(ref[t_rel:r_rel], n * G, tier.b_theta)
                 assert (th_g != th_r).sum() <= max(1, n * G // 500)
+                # radius codes equal the reference's except on a rounding boundary of the exact
+                # quotient (each mismatch checked in fp64 against the reference's own radii)
                 rc_g = got[r_rel:].view(np.int8).astype(int); rc_r = ref[r_rel:].view(np.int8).astype(int)
-                assert np.abs(rc_g - rc_r).max() <= 1 and (rc_g != rc_r).mean() < 0.02
+                r_ref = z[f"dh{dh}_t{tier.tier_id}_n{n}_r"].astype(np.float64)
+                n_bad = radius_code_mismatches_are_boundary_cases(rc_g, rc_r, r_ref, sc_r, G)
+                assert n_bad <= max(1, n * G // 500), n_bad
 
 
 @pytest.mark.parametrize("use_scratch", [True, False])

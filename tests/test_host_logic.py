@@ -179,3 +179,62 @@ def test_kmeans_training_loop_host_logic_matches_reference():
                                               init_centers=torch.from_numpy(z[f"{name}_init"]), assign_fn=cpu_assign)
         np.testing.assert_array_equal(centers.numpy(), z[f"{name}_centers"])
         assert abs(score - float(z[f"{name}_score"])) <= 1e-7
+
+
+def test_layerpool_step_inputs_are_checked_like_the_reference_extension():
+    """The reference extension reads the step inputs with data_ptr<float>() and raises on another
+    dtype (decode_kernel.cu:100-105, 271); the drop-in LayerPool rejects half, strided and
+    wrongly sized inputs the same way instead of reading them as packed fp32."""
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "spherical-kv_b200", "dropin"))
+    import sphkv_lut
+    ok = torch.zeros(8, 128)
+    with pytest.raises(RuntimeError, match="float32"):
+        sphkv_lut._f32_ptr(ok.half(), "k_post", 8 * 128)
+    with pytest.raises(RuntimeError, match="float32"):
+        sphkv_lut._f32_ptr(ok.bfloat16(), "q_post", 8 * 128)
+    with pytest.raises(RuntimeError, match="contiguous"):
+        sphkv_lut._f32_ptr(torch.zeros(128, 8).t(), "v_new", 8 * 128)
+    with pytest.raises(RuntimeError, match="elements"):
+        sphkv_lut._f32_ptr(ok, "k_post", 4 * 128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sphkv_lut._f32_ptr(ok, "k_post", 8 * 128)
+
+
+def _golden_tokens(name):
+    """The retained-token list tests/golden/make_golden.py handed to the reference's
+    _build_per_head_pages for fixture `name` (same seeds), as plain objects."""
+    from types import SimpleNamespace
+    z = np.load(os.path.join(ROOT, "tests", "golden", "decode_backrot.npz"))
+    Hq, Hkv, dh, ctx, page_size = (int(x) for x in z[f"{name}_shape"])
+    assign = synth.make_tier_assign(1, Hkv, ctx, {1: 0.5, 2: 0.5}, seed=2)
+    toks = [SimpleNamespace(layer=0, head=h, index=t, new_tier_id=int(assign[0, h, t]), segment_id=0)
+            for h in range(Hkv) for t in range(ctx)]
+    tiers = [SimpleNamespace(tier_id=0, g=0, G=0, b_theta=0)] + [
+        SimpleNamespace(tier_id=t.tier_id, g=t.g, G=dh // t.g, b_theta=t.b_theta) for t in pkg.REFERENCE_TIERS]
+    return z, toks, tiers, (Hq, Hkv, dh, ctx, page_size)
+
+
+@pytest.mark.parametrize("name", ["c1_mini", "dh128_mini"])
+def test_per_head_page_plan_matches_reference_order_and_pointer_tables(name):
+    """first-seen tier order per head, ascending positions and the (page, theta, radius) offsets
+    of every page equal what the reference's _build_per_head_pages produced
+    (spherical_kv_pipeline.py:1146-1228)"""
+    from importlib import import_module
+    php = import_module("spherical-kv_b200.per_head_pages")
+    z, toks, tiers, (Hq, Hkv, dh, ctx, page_size) = _golden_tokens(name)
+    codebooks = {(0, h, t.tier_id): None for h in range(Hkv) for t in pkg.REFERENCE_TIERS}
+    plan = php.plan_per_head_pages(toks, tiers, codebooks, page_size)
+    assert list(plan) == [(0, h) for h in range(Hkv)]
+    for h in range(Hkv):
+        entries = plan[(0, h)]
+        assert len(entries) == int(z[f"{name}_nentries_h{h}"])
+        for e, ent in enumerate(entries):
+            assert ent["tier"].b_theta == int(z[f"{name}_btheta_h{h}_e{e}"])
+            np.testing.assert_array_equal(ent["index"].numpy(), z[f"{name}_positions_h{h}_e{e}"])
+            np.testing.assert_array_equal(ent["ptable"].numpy(), z[f"{name}_ptable_h{h}_e{e}"])
+            assert ent["nbytes"] == z[f"{name}_pages_h{h}_e{e}"].size
+    # a group without a codebook is skipped, as at spherical_kv_pipeline.py:1167-1172
+    del codebooks[(0, 0, 1)]
+    plan = php.plan_per_head_pages(toks, tiers, codebooks, page_size)
+    assert [e["tier_id"] for e in plan[(0, 0)]] == [2]

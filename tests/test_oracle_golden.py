@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from util import GOLDEN, load_oracle, load_pkg
+from util import radius_code_mismatches_are_boundary_cases, GOLDEN, load_oracle, load_pkg
 
 orc = load_oracle()
 pkg = load_pkg()
@@ -65,9 +65,12 @@ def test_encode_and_page_match_reference(dh, tier, n):
     if len(diff) == 0:
         assert np.array_equal(page2[:2], page_ref[:2])
         assert np.array_equal(page2[t_rel:r_rel], page_ref[t_rel:r_rel])
+    # radius codes: the reference's norms differ from the fixed-order ones by a few ulps, so a
+    # code may differ only where the exact quotient sits on a rounding boundary (checked in fp64)
     rc, rc_ref = page2[r_rel:].view(np.int8).astype(int), page_ref[r_rel:].view(np.int8).astype(int)
-    assert np.abs(rc - rc_ref).max() <= 1
-    assert (rc != rc_ref).mean() < 0.02
+    sc_ref = page_ref[8:t_rel].view(np.float32)
+    n_bad = radius_code_mismatches_are_boundary_cases(rc, rc_ref, r_ref.astype(np.float64), sc_ref, G)
+    assert n_bad <= max(1, n * G // 500), n_bad
     # parse_page inverts build_page
     tid, cnt, sc, th_back, r_back = orc.parse_page(page_ref, 0, t_rel, r_rel, G, tier.b_theta, 0)
     assert tid == tier.tier_id and cnt == n and np.array_equal(th_back, th_ref)

@@ -22,7 +22,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _params(q, cache, rope, out, scratch):
+def _params(q, cache, rope, out, scratch, status):
     lib = pkg._lib
     L = cache.lists
     p = lib.DecodeParams()
@@ -31,6 +31,7 @@ def _params(q, cache, rope, out, scratch):
     p.block_table, p.bits_table = L.block_table.data_ptr(), L.bits_table.data_ptr()
     p.num_blocks, p.codebooks = L.num_blocks.data_ptr(), cache.codebooks.data_ptr()
     p.rope_table, p.out = rope.data_ptr(), out.data_ptr()
+    p.status = status.data_ptr()
     if scratch is not None:
         p.scratch, p.scratch_bytes = scratch.data_ptr(), scratch.numel()
     p.B, p.Hq, p.Hkv, p.dh = q.shape[0], q.shape[1], L.Hkv, q.shape[2]
@@ -61,14 +62,26 @@ def test_static_scratch_decode_matches_regular_entry_point_twice():
     scratch = pkg.decode_scratch(cache)
     stream = torch.cuda.current_stream().cuda_stream
     q2 = synth.make_kvq(B, Hq, Hkv, dh, ctx, seed=99)[2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
     for q in (Q.to(DEV), q2.to(DEV)):       # two calls in a row on the shared array
         want = torch.empty(B, Hq, dh, device=DEV)
         got = torch.full((B, Hq, dh), float("nan"), device=DEV)
-        p_ref = _params(q, cache, rope, want, scratch)
-        p_new = _params(q, cache, rope, got, None)
+        p_ref = _params(q, cache, rope, want, scratch, status)
+        p_new = _params(q, cache, rope, got, None, status)
         pkg._lib.check(lib.sphkv_decode_paged(C.byref(p_ref), stream), "sphkv_decode_paged")
+        torch.cuda.synchronize()
+        # what the name promises: the call takes no device memory, neither from the driver (free
+        # memory as cudaMemGetInfo reports it) nor from torch's caching allocator
+        free_before = torch.cuda.mem_get_info()[0]
+        stats_before = torch.cuda.memory_stats()
         pkg._lib.check(lib.sphkv_decode_paged_static(C.byref(p_new), stream), "sphkv_decode_paged_static")
         torch.cuda.synchronize()
+        stats_after = torch.cuda.memory_stats()
+        assert torch.cuda.mem_get_info()[0] == free_before
+        for key in ("allocation.all.allocated", "segment.all.allocated", "allocated_bytes.all.current",
+                    "reserved_bytes.all.current"):
+            assert stats_after[key] == stats_before[key], key
+        assert int(status.item()) == 0
         assert torch.isfinite(got).all()
         # same kernels, same work split: the tolerance of the decode parity tests (2e-3) is
         # far from needed, the results are expected to be identical
