@@ -63,9 +63,10 @@ typedef struct sphkv_tiers {
  * Builds the cos/sin table the decode kernel gathers per key position.  Values are
  * cos/sin of the fp32 product float(pos) * inv_freq[i], the same arguments the HF
  * rotary module produces for the reference's tables
- * (spherical_kv_pipeline.py:1591-1610).  Layout: f32 [max_pos][dh] where a row holds,
- * for each 16-frequency block s and lane quad j, {cos f0..f3, sin f0..f3} with
- * f = 16 s + {2j, 2j+1, 2j+8, 2j+9}.  inv_freq: device f32 [dh/2]. */
+ * (spherical_kv_pipeline.py:1591-1610).  Layout: f32 [max_pos][dh], 32-byte aligned; a row
+ * holds, for i = 0 .. dh/32 - 1 and j = 0 .. 3, {cos f0..f3, sin f0..f3} of the frequencies
+ * f = (dh/8) j + 4 ((i xor j) mod dh/32) + {0..3} (the order in which the decode kernel's
+ * lanes consume them).  inv_freq: device f32 [dh/2]. */
 int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh, const float* inv_freq,
                            void* stream);
 
@@ -140,7 +141,8 @@ int sphkv_pages_from_codes(const sphkv_encode_params* p, void* stream);
  * (call sites spherical_kv_pipeline.py:1109-1125). */
 typedef struct sphkv_decode_params {
   const void* q;              /* [B][Hq][dh] q_dtype, post-RoPE at the query position */
-  const uint8_t* k_pages;     /* byte pool                                            */
+  const uint8_t* k_pages;     /* byte pool, readable up to the next multiple of 4 bytes
+                                 past the end of its last page                        */
   const int32_t* ptable;      /* [P][3]                                               */
   const void* v_pool;         /* [P][page_size][dh] v_dtype (F16/BF16); slots past a
                                  page's count must hold finite values (zero-filled)   */

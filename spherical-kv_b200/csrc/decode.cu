@@ -1,23 +1,33 @@
 // Angle-domain decode attention over bit-packed, paged, codebook-quantised keys.
 //
-// One persistent CTA per SM walks a contiguous range of (KV head, batch row) blocks.  Each
-// warp owns every kWarps-th 16-token tile of the range and keeps an online-softmax state for
+// One persistent CTA per SM (8 warps) walks a contiguous range of (KV head, batch row) blocks.
+// Each warp owns every 8th 16-token tile of the range and keeps an online-softmax state for
 // all query heads of the KV head.
 //
 // Lane map of a tile (lane = 4 r + j): rows r and r + 8 are the lane's two tokens; in each
 // rotary half the lane owns the contiguous block of W = dh / 8 dimensions  W j .. W j + W - 1
 // and, in the other half, the same block shifted by dh / 2 -- the RoPE partner of every value
 // a lane holds is in the same lane, and for g = 16, dh = 128 a lane needs exactly two centroid
-// indices and two radii per token, which it extracts itself from the page bytes.  Per tile a warp
-//   1. reads its code / radius words straight from the page (issued one tile earlier),
+// indices and two radii per token, which it extracts itself from the page bytes.
+//
+// Data movement, all asynchronous and issued tiles ahead of use:
+//   * V tiles: tensor-map (TMA) copies into a per-warp ring, 128-byte swizzle = the pattern
+//     ldmatrix wants, completion on an mbarrier per stage (bounded wait);
+//   * page bytes + key positions: cp.async (16-byte chunks for 16-byte-aligned pages, 4-byte
+//     words otherwise) into a per-warp ring of 512-byte stages, three tiles ahead, so the
+//     page -> position -> cos/sin dependency never stalls a tile;
+//   * cos/sin rows of the key positions: one 256-bit load per (token, 4-frequency chunk) from the
+//     L2-resident table into registers, one tile ahead.
+// Per tile a warp
+//   1. extracts its centroid indices / radii from the staged page with constants that are
+//      recomputed only when the tier changes,
 //   2. gathers the selected centroid rows from shared memory (128-bit loads, chunk order
-//      skewed by j so the four lanes of a token never meet in a bank), scales by the radius
-//      and rotates by the key's RoPE angle; the cos/sin rows of the key positions arrive in
-//      shared memory by bulk async copies issued half a tile ahead,
-//   3. feeds the rotated values to the tensor cores as TF32 hi + lo parts
+//      XOR-skewed by j so the four lanes of a token never meet in a bank; odd token rows read a
+//      second copy of the codebook so the two tokens of a quarter-warp do not meet either),
+//      scales by the radius and rotates by the key's RoPE angle with packed fp32 arithmetic,
+//   3. feeds the rotated values to the tensor cores as bf16 hi + lo parts
 //      (tokens x dh) * (dh x heads), fp32 accumulate, query fragments held in registers,
-//   4. runs the online softmax and accumulates V^T P^T; V tiles are fetched by the tensor
-//      memory accelerator (2-D tiled copies with the 128-byte swizzle ldmatrix wants).
+//   4. runs the online softmax and accumulates V^T P^T.
 // Warp states are merged per CTA, CTA partials land in scratch, and a small kernel merges
 // them by log-sum-exp.
 //
@@ -40,28 +50,12 @@ namespace sphkv {
 #define SPHKV_WARPS 8
 #endif
 constexpr int kWarps = SPHKV_WARPS;
+constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
+constexpr int kMaxUnitsInKernelPlan = 2048;
 #ifndef SPHKV_VSTAGES
 #define SPHKV_VSTAGES 3
 #endif
 constexpr int kVStages = SPHKV_VSTAGES;  // V tile buffers per warp: one being read, the others in flight
-constexpr int kMetaRing = 32;  // tiles of metadata per warp, refilled 16 at a time
-constexpr int kMaxUnitsInKernelPlan = 2048;
-// operand split of the QK^T contraction: 2 = TF32 hi + lo (m16n8k8), 1 = bf16 hi + lo by
-// truncation (m16n8k16)
-#ifndef SPHKV_SPLIT
-#define SPHKV_SPLIT 2
-#endif
-constexpr int kSplit = SPHKV_SPLIT;
-// cos/sin rows: 1 = bulk async copies into shared memory, 0 = 128-bit loads into registers
-#ifndef SPHKV_CS_STAGED
-#define SPHKV_CS_STAGED 1
-#endif
-constexpr bool kCsStaged = SPHKV_CS_STAGED != 0;
-// second, bank-disjoint copy of a g = 16 codebook for odd token rows: 0 never, 1 for
-// slots of at most 16 centroids, 2 for every slot that fits
-#ifndef SPHKV_CB_DUP
-#define SPHKV_CB_DUP 1
-#endif
 
 // 16 bytes per tile
 struct TileMeta {
@@ -90,12 +84,9 @@ struct DecodeArgs {
 
 // shared-memory carve-up, shared by host and device
 __host__ __device__ constexpr int smem_v_bytes(int dh) { return kWarps * kVStages * 16 * dh * 2; }
-// one half of a cos/sin row (dh * 2 bytes) per token, 16 bytes of padding so that the two
-// tokens a quarter-warp reads sit in different banks
-__host__ __device__ constexpr int cs_pitch(int dh) { return dh * 2 + 16; }
-__host__ __device__ constexpr int smem_cs_bytes(int dh) { return kCsStaged ? kWarps * 2 * 16 * cs_pitch(dh) : 0; }
-// per warp: P^T buffer, tile metadata ring, mbarriers (kVStages for V, two for cos/sin)
-__host__ __device__ constexpr int smem_priv_bytes() { return 512 + kMetaRing * 16 + 64; }
+// per warp: P^T buffer, tile metadata ring, mbarriers (kVStages for V, two for cos/sin), four
+// 512-byte stages of page pieces + positions
+__host__ __device__ constexpr int smem_priv_bytes() { return 512 + kMetaRing * 16 + 64 + 4 * 512; }
 
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -138,12 +129,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-// one row segment, global -> this CTA's shared memory, completion counted on an mbarrier
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
 // one box of a 2-D tensor map, global -> this CTA's shared memory
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
@@ -151,28 +136,22 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void mma_tf32_1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
+// codebook rows only: they do not change while a segment is processed, so the load may be
+// scheduled freely
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
   float4 v;
-  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  asm("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
 
 // ---- RoPE table ------------------------------------------------------------------------
 // Row of one position: for loop index i (0 .. W/4 - 1) and lane quad member j (0 .. 3) the
-// four frequencies  W j + 4 ((i + j) mod (W/4)) + {0..3}  as {cos x 4, sin x 4}: 32 bytes per
+// four frequencies  W j + 4 ((i xor j) mod (W/4)) + {0..3}  as {cos x 4, sin x 4}: 32 bytes per
 // (i, j), so what the four lanes of a token read in one step is one 128-byte line, and the
 // first half of the row is what the first half of the tile loop needs.
 __host__ __device__ __forceinline__ int lane_freq(int dh, int i, int j, int e) {
   const int W = dh / 8, nch = W / 4;
-  return W * j + 4 * ((i + j) & (nch - 1)) + e;
+  return W * j + 4 * ((i ^ j) & (nch - 1)) + e;
 }
 __global__ void rope_table_kernel(float* __restrict__ table, int max_pos, int dh,
                                   const float* __restrict__ inv_freq) {
@@ -246,37 +225,56 @@ __device__ __forceinline__ int find_unit(const int32_t* pfx, int n, int64_t x) {
   return lo;
 }
 
-// Page words a lane needs for its two tokens (index = 2 * token + rotary half): the aligned
-// 32-bit word holding the start of the centroid index (and the next one when the index
-// straddles it), the word(s) holding the radius, and the two per-group scales.
-// The positions of the two tokens ride along.  Three of these rotate through the tile loop
-// (tile k is consumed while the loads of tiles k + 1 and k + 2 are in flight); the loop is
-// unrolled by three so that each set keeps its registers: copying a set forward would make
-// every iteration wait for loads it has only just issued.
-struct KRaw {
-  uint32_t tw0[4], tw1[4], rw0[4], rw1[4];
-  float sc[2];
-  int pos[2];
-};
+// ---- K stage: what a tile needs of its page, copied into a per-warp ring ---------------------
+// A stage holds, at fixed offsets, the page header + group scales, the slice of the theta bit
+// stream of the tile's 16 tokens, the slice of their radius bytes and their 16 positions.
+// Every piece starts at the 4-byte word that holds its first byte, so the byte phase inside
+// the first word is the phase the piece has in the pool.  The copies are 4-byte cp.async
+// (the pool only promises 4-byte alignment), word w of the stage by lane w mod 32 in round
+// w / 32; they are issued three tiles ahead and cost no registers while in flight.
+constexpr int kKStages = 4;
+constexpr int kKStageBytes = 512;
+constexpr int kKHdr = 0;    // 12 words: 8 header bytes + up to 8 scales (+ slack)
+constexpr int kKTh = 48;    // 28 words: 16 tokens x 8 groups x 6 bits = 96 bytes + phase
+constexpr int kKRd = 160;   // 68 words: 16 tokens x 8 groups x 2 bytes = 256 bytes + phase
+constexpr int kKPos = 448;  // 16 words
+static_assert(kKPos + 64 <= kKStageBytes, "K stage layout");
+
+__device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gptr));
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ int lds_s8(uint32_t addr) {
+  int v;
+  asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
 // PACK (<= 4 query heads per KV head): the 8 mma columns carry [q_hi heads 0..3 | q_lo heads
 // 0..3] (one product fewer per step) and later [P_hi | P_lo] (one product per V tile).
-template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
+// MODE 0: 16-token pages with int8 radii and no side outputs (the serving configuration: page
+// size and radius format are compile-time constants); 1: any page size / radius format;
+// 2: as 1, plus the logits / per-tile statistics side outputs.
+template <int DH, typename VT, bool ROT, int MODE, bool PACK>
 __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
+  constexpr bool EXTRA = MODE == 2, FAST = MODE == 0;
   constexpr int KS = DH / 16;   // 16-dim output tiles of the V product
   constexpr int W = DH / 8;     // dims a lane owns in each rotary half
   constexpr int NCH = W / 4;    // 16-byte chunks of those dims
-  constexpr int NH = NCH / 2;   // chunks per half of the tile loop
   constexpr int V_TILE = 16 * DH * 2;
   constexpr int V_WARP = kVStages * V_TILE;
-  constexpr int CS_PITCH = cs_pitch(DH);
-  constexpr int CS_HALF = 16 * CS_PITCH;
   constexpr bool kBf16 = std::is_same<VT, __nv_bfloat16>::value;
-  constexpr bool STAGED = ROT && kCsStaged;
-  // query fragment registers per (rotary half, chunk): TF32 two k8 steps x {b0, b1}, bf16 one k16 step
-  constexpr int QR = kSplit == 2 ? 4 : 2;
 
   extern __shared__ __align__(1024) uint8_t smem[];
   const sphkv_decode_params& p = a.p;
@@ -284,27 +282,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
   const int r = lane >> 2, j = lane & 3;
 
   uint8_t* v_ring = smem + warp * V_WARP;
-  uint8_t* cs_warp = smem + smem_v_bytes(DH) + warp * 2 * CS_HALF;
-  uint8_t* cb_smem = smem + smem_v_bytes(DH) + smem_cs_bytes(DH);
+  uint8_t* cb_smem = smem + smem_v_bytes(DH);
   uint8_t* warp_priv = cb_smem + a.cb_smem_bytes + warp * smem_priv_bytes();
   uint16_t* pbuf = reinterpret_cast<uint16_t*>(warp_priv);  // [2][8][16]
   TileMeta* meta = reinterpret_cast<TileMeta*>(warp_priv + 512);
   const uint32_t bar_v = smem_u32(warp_priv + 512 + kMetaRing * 16);  // one per V stage
-  const uint32_t bar_cs = bar_v + 8 * kVStages;                        // two cos/sin halves
-  static_assert(8 * (kVStages + 2) <= 64, "mbarriers exceed their slot");
+  static_assert(8 * kVStages <= 64, "mbarriers exceed their slot");
+  const uint32_t k_ring = bar_v + 64;  // kKStages stages of kKStageBytes
   const uint32_t cb_u32 = smem_u32(cb_smem);
-  const uint32_t cs_lane = smem_u32(cs_warp) + r * CS_PITCH + j * 32;
 
   if (lane == 0) {
 #pragma unroll
     for (int i = 0; i < kVStages; ++i) mbar_init(bar_v + 8 * i, 1);
-    mbar_init(bar_cs, 1);
-    mbar_init(bar_cs + 8, 1);
     fence_async_smem();
   }
   __syncthreads();
   // V ring position of the next tile to issue / to wait for: stage index and phase parity
-  uint32_t vi_stage = 0, vw_stage = 0, vw_phase = 0, cs_waited[2] = {0, 0};
+  uint32_t vi_stage = 0, vw_stage = 0, vw_phase = 0;
   bool dead = false;  // a bounded wait ran out: stop working, keep meeting the CTA barriers
 
   // ---- block prefix per unit: computed by warp 0 of every CTA (CTA 0 publishes it for the
@@ -348,12 +342,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
   if (start >= end) return;
   int u = find_unit(pfx, a.n_units, start);
 
-  const int N = p.page_size;
+  const int N = FAST ? 16 : p.page_size;
   const int TPP = N >> 4;  // 16-token tiles per page: 1, 2, 4 or 8
   const int tpp_shift = 31 - __clz(TPP);
   const float qscale = p.sm_scale * kLog2e;
-  const int fmt = p.radius_fmt;
-  const int rb = fmt == SPHKV_RADIUS_F16 ? 2 : 1;
+  const int fmt = FAST ? SPHKV_RADIUS_I8 : p.radius_fmt;
+  const uint32_t rb = fmt == SPHKV_RADIUS_F16 ? 2u : 1u;
   int cb_head_loaded = -1;
   // per tier slot: b_theta | log2(g) << 8 | duplicated << 12 | codebook offset in shared
   // memory << 13, held by lanes 0..3 and read with a shuffle
@@ -367,10 +361,65 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
                 ((uint32_t)off_l << 13);
   }
   auto tier_of = [&](int slot) { return __shfl_sync(0xffffffffu, tier_word, slot); };
-  // chunk order of this lane: loop index i reads chunk (i + j) mod NCH of its centroid rows
-  uint32_t coff[NCH];
+  // chunk order of this lane: loop index i reads chunk (i xor j) mod NCH of its centroid rows,
+  // i.e. byte (row ^ (j mod NCH) * 16) ^ (i * 16) of a 64-byte-aligned row
+  const uint32_t cskew = (uint32_t)((j & (NCH - 1)) * 16);
+
+  // ldmatrix row address of this lane for output tile dt: token row tau, 16-byte chunk
+  // c = 2 dt + (lane / 8 & 1) of the 256-byte row, stored at chunk (c & 7) ^ (tau & 7) of the
+  // 128-byte half-row (c >> 3).  (c & 7) ^ (tau & 7) = 2 (dt & 3) ^ ((lane / 8 & 1) ^ (tau & 7)).
+  uint32_t ldsm_off[4];
+  {
+    const int mi = lane >> 3, tau = (lane & 7) + ((mi >> 1) << 3);
 #pragma unroll
-  for (int i = 0; i < NCH; ++i) coff[i] = (uint32_t)(((i + j) & (NCH - 1)) * 16);
+    for (int x = 0; x < 4; ++x) ldsm_off[x] = (uint32_t)(tau * 128 + (((2 * x) ^ ((mi & 1) ^ (tau & 7))) << 4));
+  }
+  // K-stage copy plan of this lane: in round q it copies stage word 32 q + lane.  Words 0..11
+  // are the header piece, 12..39 the theta piece, 40..107 the radius piece, 108..123 the
+  // positions; krel[q] is the byte offset of the lane's word inside its piece.
+  const uint32_t krel[4] = {4u * (lane < 12 ? lane : lane - 12), 4u * (lane < 8 ? lane + 20 : lane - 8),
+                            4u * (lane + 24), 4u * (lane < 12 ? lane + 56 : lane - 12)};
+  uint32_t k_issue = 0;  // K stages issued so far (ring index = k_issue mod kKStages)
+  uint32_t k_read = 0;   // K stages consumed so far
+
+  // lane constants of the tier slot of the current tile, recomputed only when the slot changes
+  // (block lists keep the pages of a tier together)
+  int c_slot = -1;
+  uint32_t c_bits = 1, c_mask = 1, c_rowb = 64, c_cb_lo = 0, c_cb_hi = 0;
+  // bit offset of the centroid index of (token, half) and byte offset of its radius: relative to
+  // the tile's theta / radius slice, or (FAST) to the page start and to the first radius byte
+  uint32_t c_bit[4] = {0, 0, 0, 0};
+  uint32_t c_wa[4] = {0, 0, 0, 0};    // FAST: byte offset in the stage of the word holding the index
+  uint32_t c_rad[4] = {0, 0, 0, 0};
+  uint32_t c_sc[2] = {0, 0};          // byte offset of its group's scale in the header piece
+  auto load_slot_constants = [&](int slot) {
+    const uint32_t tw = tier_of(slot);
+    const int lg = (tw >> 8) & 0xF;
+    const int G = DH >> lg;
+    const int glo = (W * j) >> lg, ghi = glo + (G >> 1);
+    const int sub_off = (W * j) & ((1 << lg) - 1);
+    const int dup = (tw >> 12) & 1;
+    c_bits = tw & 0xFF;
+    c_mask = (1u << c_bits) - 1u;
+    c_rowb = 4u << (lg + dup);  // bytes from one centroid row to the next
+    const uint32_t base = cb_u32 + (tw >> 13) + sub_off * 4 + (dup ? (r & 1) * 64 : 0);
+    c_cb_lo = base + ((uint32_t)glo << c_bits) * c_rowb;
+    c_cb_hi = base + ((uint32_t)ghi << c_bits) * c_rowb;
+#pragma unroll
+    for (int tk = 0; tk < 2; ++tk)
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const uint32_t idx = (uint32_t)((r + 8 * tk) * G + (hf ? ghi : glo));
+        // 16-token pages: the theta stream starts 8 + 4 G bytes into the page (pagebuilder.py:8-33;
+        // checked against the pointer table when the tile metadata is fetched)
+        c_bit[2 * tk + hf] = idx * c_bits + (FAST ? (8 + 4 * G) * 8 : 0);
+        c_wa[2 * tk + hf] = (c_bit[2 * tk + hf] >> 5) << 2;
+        c_rad[2 * tk + hf] = idx * rb;
+      }
+    c_sc[0] = 8 + 4 * glo;
+    c_sc[1] = 8 + 4 * ghi;
+    c_slot = slot;
+  };
 
   while (start < end) {
     while ((int64_t)pfx[u + 1] <= start) ++u;  // skip units without blocks
@@ -431,6 +480,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         const uint32_t hdr = *reinterpret_cast<const uint32_t*>(p.k_pages + mf_poff);
         count = (int)((hdr >> 8) & 0xFFu);
         if (count > N) count = N;
+        if (FAST && mf_toff - mf_poff != 8 + 4 * (DH / p.tiers.g[mf_slot])) {
+          // the pointer table disagrees with the page format: not a page this path can read
+          if (p.status) atomicOr(p.status, SPHKV_ST_BAD_BLOCK);
+          m.phys = -1;
+          count = 0;
+        }
       }
       m.misc = (uint32_t)((mf_roff - mf_toff) & 0xFFFF) | ((uint32_t)count << 16) | ((uint32_t)mf_slot << 24);
       meta[(kbase + lane) & (kMetaRing - 1)] = m;
@@ -469,105 +524,108 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
       return ok;
     };
 
-    // geometry of this lane's two groups for a tier word
-    auto lane_groups = [&](uint32_t tw, int& G, int& glo, int& ghi, int& sub_off) {
-      const int lg = (tw >> 8) & 0xF;
-      G = DH >> lg;
-      glo = (W * j) >> lg;
-      ghi = glo + (G >> 1);
-      sub_off = (W * j) & ((1 << lg) - 1);
-    };
-
-    auto load_kraw = [&](int kk, KRaw& w) {
+    // One K stage per tile, issued three tiles ahead.  16-token pages: the page image itself,
+    // word for word from the page start (header at 0, theta at toff - poff, radii at
+    // roff - poff).  Larger pages: the header piece at kKHdr, the tile's slice of the theta
+    // stream at kKTh and of the radii at kKRd, each from the word that holds its first byte.
+    // The positions go to kKPos.  One commit group per call, whether or not anything is
+    // copied, so that the group of tile k is always the (kKStages - 1)-th newest when tile k
+    // is consumed.
+    auto issue_k = [&](int kk) {
+      if (kk < nt) {
+        const TileMeta m = get_meta(kk);
+        const uint32_t dst = k_ring + (k_issue & (kKStages - 1)) * kKStageBytes + 4 * lane;
+        if (m.phys >= 0) {
+          const uint32_t tw = tier_of(meta_slot(m));
+          const uint32_t bits = tw & 0xFF, G = (uint32_t)DH >> ((tw >> 8) & 0xF);
+          const uint32_t poff = (uint32_t)m.poff;
+          if (TPP == 1) {
+            const uint32_t page_end = (uint32_t)meta_roff(m) + (uint32_t)meta_count(m) * G * rb;
+            if ((poff & 15u) == 0) {
+              // 16-byte copies for the chunks wholly inside the page (at most 24), 4-byte copies by
+              // the next four lanes for the words of the last, partial chunk: nothing past the page
+              const uint32_t full = (page_end - poff) >> 4;
+              const uint32_t kb = dst - 4 * lane;
+              if ((uint32_t)lane < full) {
+                cp_async_16(kb + 16 * lane, p.k_pages + (poff + 16 * lane));
+              } else {
+                const uint32_t o = 16 * full + 4 * (lane - full);
+                if (lane < full + 4 && poff + o < page_end) cp_async_4(kb + o, p.k_pages + (poff + o));
+              }
+            } else {
+              const uint32_t off = poff + 4 * lane;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) w.tw0[i] = w.tw1[i] = w.rw0[i] = w.rw1[i] = 0u;
-      w.sc[0] = w.sc[1] = 0.f;
-      w.pos[0] = w.pos[1] = -1;
-      if (kk >= nt) return;
-      const TileMeta m = get_meta(kk);
-      if (m.phys < 0) return;
-      if (ROT) {  // key positions of rows r and r + 8 (-1: no token)
-        const int32_t* pp = p.positions + (int64_t)m.phys * N + 16 * tile_sub(kk);
-        w.pos[0] = pp[r];
-        w.pos[1] = pp[r + 8];
-      }
-      const uint32_t tw = tier_of(meta_slot(m));
-      const int bits = tw & 0xFF;
-      int G, glo, ghi, sub_off;
-      lane_groups(tw, G, glo, ghi, sub_off);
-      const int roff = meta_roff(m);
-#pragma unroll
-      for (int tk = 0; tk < 2; ++tk) {
-        const int tp = 16 * tile_sub(kk) + r + 8 * tk;
-        if (tp >= meta_count(m)) continue;
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int idx = tp * G + (hf ? ghi : glo);
-          const int bit = idx * bits;
-          const int ba = m.toff + (bit >> 3);
-          const uint32_t* wp = reinterpret_cast<const uint32_t*>(p.k_pages + (ba & ~3));
-          w.tw0[2 * tk + hf] = wp[0];
-          if ((ba & 3) * 8 + (bit & 7) + bits > 32) w.tw1[2 * tk + hf] = wp[1];
-          const int ra = roff + idx * rb;
-          const uint32_t* rp = reinterpret_cast<const uint32_t*>(p.k_pages + (ra & ~3));
-          w.rw0[2 * tk + hf] = rp[0];
-          if (rb == 2 && (ra & 3) == 3) w.rw1[2 * tk + hf] = rp[1];
+              for (int q = 0; q < 3; ++q)
+                if (off + 128 * q < page_end) cp_async_4(dst + 128 * q, p.k_pages + (off + 128 * q));
+              if (rb == 2 && off + 384 < page_end && lane < 16) cp_async_4(dst + 384, p.k_pages + (off + 384));
+            }
+          } else {
+            const int sub = tile_sub(kk);
+            const uint32_t t0 = 16u * sub, t1 = min((uint32_t)meta_count(m), t0 + 16u);
+            const uint32_t th0 = (uint32_t)m.toff + ((t0 * G * bits) >> 3);
+            const uint32_t th1 = (uint32_t)m.toff + ((t1 * G * bits + 7) >> 3);
+            const uint32_t rd0 = (uint32_t)meta_roff(m) + t0 * G * rb, rd1 = (uint32_t)meta_roff(m) + t1 * G * rb;
+            const uint32_t hdr1 = poff + 8 + 4 * G, thA = th0 & ~3u, rdA = rd0 & ~3u;
+            {  // words 0..31: header | theta
+              const bool hd = lane < 12;
+              const uint32_t off = (hd ? poff : thA) + krel[0];
+              if (off < (hd ? hdr1 : th1)) cp_async_4(dst, p.k_pages + off);
+            }
+            {  // words 32..63: theta | radius
+              const bool th = lane < 8;
+              const uint32_t off = (th ? thA : rdA) + krel[1];
+              if (off < (th ? th1 : rd1)) cp_async_4(dst + 128, p.k_pages + off);
+            }
+            {  // words 64..95: radius
+              const uint32_t off = rdA + krel[2];
+              if (off < rd1) cp_async_4(dst + 256, p.k_pages + off);
+            }
+            if (lane < 12) {  // words 96..107: radius
+              const uint32_t off = rdA + krel[3];
+              if (off < rd1) cp_async_4(dst + 384, p.k_pages + off);
+            }
+          }
+          if (ROT && lane >= 16)  // words 112..127: positions
+            cp_async_4(dst + 384, p.positions + ((uint32_t)m.phys * (uint32_t)N + 16u * tile_sub(kk) + (lane - 16)));
+        } else if (ROT && lane >= 16) {
+          // a hole in the block list: no page; its positions read as "no token"
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst + 384), "r"(0xFFFFFFFFu) : "memory");
         }
       }
-      if (rb == 1) {
-        const float* sp = reinterpret_cast<const float*>(p.k_pages + m.poff + 8);
-        w.sc[0] = sp[glo];
-        w.sc[1] = sp[ghi];
-      }
-    };
-    auto clamp_pos = [&](int pos) -> int {
-      if (pos >= p.max_pos) {
-        if (p.status) atomicOr(p.status, SPHKV_ST_BAD_POSITION);
-        pos = 0;
-      }
-      return pos < 0 ? 0 : pos;
+      cp_async_commit();
+      ++k_issue;
     };
 
-    // cos/sin of the tile's key positions.  Staged: half h of the row (loop indices
-    // h * NH .. h * NH + NH - 1) of every token goes to shared memory by one bulk copy per
-    // token, lanes with j = 0 for rows r, j = 1 for rows r + 8.  Register path: this lane's
-    // 32-byte pieces by 128-bit loads through L1.
-    float4 cs[STAGED ? 1 : 2][STAGED ? 1 : NCH][2];
-    auto issue_cs_half = [&](int h, const int (&ps)[2]) {
-      if constexpr (STAGED) {
-        const int pos = j == 0 ? ps[0] : ps[1];
-        const bool mine = j < 2 && pos >= 0;
-        const uint32_t n_rows = __popc(__ballot_sync(0xffffffffu, mine));
-        const uint32_t bar = bar_cs + 8 * h;
-        if (lane == 0) mbar_expect_tx(bar, n_rows * (DH * 2));
-        __syncwarp();
-        if (mine) {
-          const int row = r + 8 * j;
-          bulk_copy_g2s(smem_u32(cs_warp) + h * CS_HALF + row * CS_PITCH,
-                        p.rope_table + (int64_t)clamp_pos(pos) * DH + h * (DH / 2), DH * 2, bar);
-        }
-      }
+    // table row of a key position: "no token" (-1) and out-of-range positions read row 0; the
+    // latter also raise a status bit
+    auto clamp_pos = [&](int pos) -> uint32_t {
+      if (pos >= p.max_pos && p.status) atomicOr(p.status, SPHKV_ST_BAD_POSITION);
+      return (uint32_t)pos < (uint32_t)p.max_pos ? (uint32_t)pos : 0u;
     };
-    auto issue_cs_regs = [&](const int (&ps)[2]) {
-      if constexpr (ROT && !STAGED) {
+    // positions of this lane's two tokens in K stage `st` (-1: no token)
+    auto stage_pos = [&](uint32_t st, int (&ps)[2]) {
+      ps[0] = (int)lds32(st + kKPos + 4 * r);
+      ps[1] = (int)lds32(st + kKPos + 4 * r + 32);
+    };
+
+    // cos/sin of this lane's two key positions: one 256-bit load per (token, chunk) brings the
+    // chunk's {cos x 4, sin x 4} (the table is L2 resident), issued for tile k + 1 once tile k
+    // has used its own
+    float4 cs[2][NCH][2];
+    auto issue_cs = [&](const int (&ps)[2]) {
+      if constexpr (ROT) {
 #pragma unroll
         for (int tk = 0; tk < 2; ++tk) {
-          const float4* rp = reinterpret_cast<const float4*>(p.rope_table + (int64_t)clamp_pos(ps[tk]) * DH) + j * 2;
+          const float4* rp = reinterpret_cast<const float4*>(p.rope_table) + (clamp_pos(ps[tk]) * (DH / 4) + j * 2);
 #pragma unroll
           for (int i = 0; i < NCH; ++i) {
-            cs[tk][i][0] = __ldg(rp + i * 8);
-            cs[tk][i][1] = __ldg(rp + i * 8 + 1);
+            asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=f"(cs[tk][i][0].x), "=f"(cs[tk][i][0].y), "=f"(cs[tk][i][0].z), "=f"(cs[tk][i][0].w),
+                           "=f"(cs[tk][i][1].x), "=f"(cs[tk][i][1].y), "=f"(cs[tk][i][1].z), "=f"(cs[tk][i][1].w)
+                         : "l"(rp + i * 8));
           }
         }
       }
-    };
-    auto wait_cs_half = [&](int h) -> bool {
-      bool ok = true;
-      if constexpr (STAGED) {
-        ok = mbar_wait(bar_cs + 8 * h, cs_waited[h] & 1u);
-        ++cs_waited[h];
-      }
-      return ok;
     };
 
     auto stage_codebooks = [&]() {
@@ -597,9 +655,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
     };
 
     // query fragments (B operand [k = dim][n = column]) in registers, pre-scaled by
-    // sm_scale * log2(e).  Column n of a packed tile: head n & 3, hi part for n < 4, lo part
-    // otherwise; unpacked: qh = hi parts, ql = lo parts of head n.
-    uint32_t qh[2 * NCH][QR], ql[PACK ? 1 : 2 * NCH][PACK ? 1 : QR];
+    // sm_scale * log2(e) and split into bf16 hi (truncated) + bf16 lo.  Column n of a packed tile:
+    // head n & 3, hi part for n < 4, lo part otherwise; unpacked: qh = hi parts, ql = lo parts of
+    // head n.  Chunk s of rotary half hf: register 0 = values 0, 1 (k = 2j, 2j + 1), register 1 =
+    // values 2, 3 (k = 2j + 8, 2j + 9).
+    uint32_t qh[2 * NCH][2], ql[PACK ? 1 : 2 * NCH][2];
     auto load_q = [&]() {
       const int n = r;  // B-fragment column of this lane
       const int head = PACK ? (n & 3) : n;
@@ -609,39 +669,25 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
       for (int hf = 0; hf < 2; ++hf)
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
-          float v[4], hi[4], lo[4];
+          float hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int d = hf * (DH / 2) + lane_freq(DH, i, j, e);
-            v[e] = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
-            const uint32_t msk = kSplit == 2 ? 0xFFFFE000u : 0xFFFF0000u;
-            hi[e] = __uint_as_float(__float_as_uint(v[e]) & msk);
-            lo[e] = v[e] - hi[e];
+            const float v = real ? load_as_float(p.q, p.q_dtype, qbase + d) * qscale : 0.f;
+            hi[e] = __uint_as_float(__float_as_uint(v) & 0xFFFF0000u);
+            lo[e] = v - hi[e];
           }
           const int s = hf * NCH + i;
-          if (kSplit == 2) {
-            // k8 step t: b0 = value 2t (k = j), b1 = value 2t + 1 (k = j + 4)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (PACK) {
-                qh[s][e] = __float_as_uint(n < 4 ? hi[e] : lo[e]);
-              } else {
-                qh[s][e] = __float_as_uint(hi[e]);
-                ql[PACK ? 0 : s][PACK ? 0 : e] = __float_as_uint(lo[e]);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int e2 = 0; e2 < 2; ++e2) {
-              const uint32_t h2 = __byte_perm(__float_as_uint(hi[2 * e2]), __float_as_uint(hi[2 * e2 + 1]), 0x7632);
-              __nv_bfloat162 lb = __floats2bfloat162_rn(lo[2 * e2], lo[2 * e2 + 1]);
-              const uint32_t l2 = *reinterpret_cast<uint32_t*>(&lb);
-              if (PACK) {
-                qh[s][e2] = n < 4 ? h2 : l2;
-              } else {
-                qh[s][e2] = h2;
-                ql[PACK ? 0 : s][PACK ? 0 : e2] = l2;
-              }
+          for (int e2 = 0; e2 < 2; ++e2) {
+            const uint32_t h2 = __byte_perm(__float_as_uint(hi[2 * e2]), __float_as_uint(hi[2 * e2 + 1]), 0x7632);
+            __nv_bfloat162 lb = __floats2bfloat162_rn(lo[2 * e2], lo[2 * e2 + 1]);
+            const uint32_t l2 = *reinterpret_cast<uint32_t*>(&lb);
+            if (PACK) {
+              qh[s][e2] = n < 4 ? h2 : l2;
+            } else {
+              qh[s][e2] = h2;
+              ql[PACK ? 0 : s][e2] = l2;
             }
           }
         }
@@ -668,18 +714,18 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < kVStages - 1; ++i) issue_v(i);
-    KRaw kw_a, kw_b, kw_c;  // page words of tiles k, k+1, k+2 (rotating)
-    load_kraw(0, kw_a);
-    load_kraw(1, kw_b);
-    if (nt > 0) {
-      issue_cs_half(0, kw_a.pos);
-      issue_cs_half(1, kw_a.pos);
-      issue_cs_regs(kw_a.pos);
+#pragma unroll
+    for (int i = 0; i < kKStages - 1; ++i) issue_k(i);
+    if (nt > 0 && ROT) {
+      // tile 0's positions start its cos/sin fetch
+      cp_async_wait<kKStages - 2>();
+      __syncwarp();
+      int ps0[2];
+      stage_pos(k_ring + (k_read & (kKStages - 1)) * kKStageBytes, ps0);
+      issue_cs(ps0);
     }
 
-    // one tile: `cur` holds tile k, `nx1` tile k + 1 (its positions start the next cos/sin
-    // copies), `nx2` receives the loads of tile k + 2.  Returns false when a wait gave up.
-    auto tile_step = [&](const int k, KRaw& cur, KRaw& nx1, KRaw& nx2) -> bool {
+    for (int k = 0; k < nt; ++k) {
       {  // fetch the next 16 tiles' metadata into the idle half of the ring, in three steps
         const int ph = k & 15, kb = (k & ~15) + 16;
         if (ph == 0) meta_stage0(kb);
@@ -687,120 +733,120 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         else if (ph == 10) { meta_stage2(kb); __syncwarp(); }
       }
       issue_v(k + kVStages - 1);  // into the stage tile k - 1 has just released
-      load_kraw(k + 2, nx2);
+      issue_k(k + kKStages - 1);
       const TileMeta m = get_meta(k);
       const int sub = tile_sub(k);
       const int cnt_tile = m.phys < 0 ? 0 : min(16, max(0, meta_count(m) - 16 * sub));
-      const bool live = cnt_tile > 0;
-      bool ok_wait = true;
+      // K stages of tiles k and k + 1 have landed (the two newest groups may be in flight)
+      cp_async_wait<kKStages - 2>();
+      __syncwarp();
+      const uint32_t kst = k_ring + (k_read & (kKStages - 1)) * kKStageBytes;
+      const uint32_t kst1 = k_ring + ((k_read + 1) & (kKStages - 1)) * kKStageBytes;
+      ++k_read;
+      int pos_n[2] = {-1, -1};
+      if (ROT && k + 1 < nt) stage_pos(kst1, pos_n);
+
+      if (cnt_tile == 0) {
+        // nothing stored here (a hole, or a tile past the page's count): keep the pipelines moving
+        if (EXTRA && ml_seg != nullptr && lane < a.grp) {  // its statistics: (-inf, 0)
+          float* dst = ml_seg + lane * ml_head + 2 * kWarps * k;
+          dst[0] = -INFINITY;
+          dst[1] = 0.f;
+        }
+        if (k + 1 < nt) issue_cs(pos_n);
+        uint32_t v_stage;
+        if (!__all_sync(0xffffffffu, wait_v(v_stage))) { dead = true; break; }
+        continue;
+      }
 
       // ---- this lane's centroid rows and radii for tokens r, r + 8 ------------------------
-      uint32_t row_lo[2] = {cb_u32, cb_u32}, row_hi[2] = {cb_u32, cb_u32};
-      float rad_lo[2] = {0.f, 0.f}, rad_hi[2] = {0.f, 0.f};
-      if (live) {
-        const uint32_t tw = tier_of(meta_slot(m));
-        const int bits = tw & 0xFF;
-        const uint32_t cmask = (1u << bits) - 1u;
-        const int dup = (tw >> 12) & 1;
-        const int row_shift = (int)((tw >> 8) & 0xF) + 2 + dup;
-        int G, glo, ghi, sub_off;
-        lane_groups(tw, G, glo, ghi, sub_off);
-        const uint32_t base = cb_u32 + (tw >> 13) + sub_off * 4 + (dup ? (r & 1) * 64 : 0);
-        const int roff = meta_roff(m);
+      int pos_c[2] = {0, 0};
+      if (ROT) stage_pos(kst, pos_c);
+      if (meta_slot(m) != c_slot) load_slot_constants(meta_slot(m));
+      // stage-relative byte address of the first theta byte / radius byte of the tile
+      uint32_t th_b0, rd_b0;
+      if (FAST) {
+        th_b0 = 0;  // folded into the slot constants
+        rd_b0 = (uint32_t)(m.toff - m.poff) + (m.misc & 0xFFFFu);
+      } else if (TPP == 1) {
+        th_b0 = (uint32_t)(m.toff - m.poff);
+        rd_b0 = th_b0 + (m.misc & 0xFFFFu);
+      } else {
+        const uint32_t G = (uint32_t)DH >> ((tier_of(meta_slot(m)) >> 8) & 0xF);
+        th_b0 = kKTh + (((uint32_t)m.toff + ((16u * sub * G * c_bits) >> 3)) & 3u);
+        rd_b0 = kKRd + (((uint32_t)meta_roff(m) + 16u * sub * G * rb) & 3u);
+      }
+      uint32_t row_lo[2], row_hi[2];
+      float rad_lo[2], rad_hi[2];
+      {
+        const uint32_t th_bit = th_b0 << 3;
+        const uint32_t rd_ad = kst + rd_b0;
+        float scl[2] = {1.f, 1.f};
+        if (fmt != SPHKV_RADIUS_F16) {
+          scl[0] = __uint_as_float(lds32(kst + kKHdr + c_sc[0])) * (1.0f / 127.0f);
+          scl[1] = __uint_as_float(lds32(kst + kKHdr + c_sc[1])) * (1.0f / 127.0f);
+        }
 #pragma unroll
-        for (int tk = 0; tk < 2; ++tk) {
-          const int tp = 16 * sub + r + 8 * tk;
-          const bool tok_ok = tp < meta_count(m);
+        for (int tk = 0; tk < 2; ++tk)
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
-            const int grp = hf ? ghi : glo;
-            const int idx = tp * G + grp;
-            const int bit = idx * bits;
-            const int ba = m.toff + (bit >> 3);
-            const uint32_t code =
-                __funnelshift_r(cur.tw0[2 * tk + hf], cur.tw1[2 * tk + hf], (ba & 3) * 8 + (bit & 7)) & cmask;
-            const uint32_t row = base + ((((uint32_t)grp << bits) + code) << row_shift);
-            const int ra = roff + idx * rb;
+            const uint32_t bit = th_bit + c_bit[2 * tk + hf];
+            const uint32_t wa = kst + (FAST ? c_wa[2 * tk + hf] : ((bit >> 5) << 2));
+            const uint32_t code = __funnelshift_r(lds32(wa), lds32(wa + 4), bit) & c_mask;
+            const uint32_t row = ((hf ? c_cb_hi : c_cb_lo) + code * c_rowb) ^ cskew;
             float rad;
             if (fmt == SPHKV_RADIUS_F16) {
-              const uint32_t hv = __funnelshift_r(cur.rw0[2 * tk + hf], cur.rw1[2 * tk + hf], (ra & 3) * 8);
-              rad = __half2float(__ushort_as_half((unsigned short)(hv & 0xFFFFu)));
+              const uint32_t ra = rd_ad + c_rad[2 * tk + hf];
+              rad = __half2float(__ushort_as_half((unsigned short)(lds_u8(ra) | (lds_u8(ra + 1) << 8))));
             } else {
-              const int c8 = (int)(int8_t)((cur.rw0[2 * tk + hf] >> ((ra & 3) * 8)) & 0xFFu);
-              rad = (cur.sc[hf] * (float)c8) * (1.0f / 127.0f);
+              rad = scl[hf] * (float)lds_s8(rd_ad + c_rad[2 * tk + hf]);
             }
-            if (!tok_ok) rad = 0.f;
             if (hf) { row_hi[tk] = row; rad_hi[tk] = rad; } else { row_lo[tk] = row; rad_lo[tk] = rad; }
           }
-        }
       }
 
       // ---- rebuild the rotated key tile chunk by chunk, QK^T on tensor cores ---------------
       float s_h[4] = {0.f, 0.f, 0.f, 0.f}, s_l[4] = {0.f, 0.f, 0.f, 0.f}, s_x[4] = {0.f, 0.f, 0.f, 0.f};
       auto qk_chunk = [&](int s, const float2 (&v)[2][2]) {
-        // v[token][pair]: the four values of chunk s for rows r and r + 8
-        if constexpr (kSplit == 2) {
-          uint32_t ah[2][4], al[2][4];
+        // v[token][pair]: the four values of chunk s for rows r and r + 8.  Operand split: hi = the
+        // upper 16 bits of the fp32 value (a bf16 number, by truncation: one byte permute packs two
+        // of them), lo = the value minus hi, again truncated to bf16; hi + lo carries 16 mantissa
+        // bits, and the three products hi*hi + lo*hi + hi*lo are accumulated in fp32.
+        uint32_t ah[4], al[4];
 #pragma unroll
-          for (int tk = 0; tk < 2; ++tk)
+        for (int tk = 0; tk < 2; ++tk)
 #pragma unroll
-            for (int e2 = 0; e2 < 2; ++e2) {
-              const uint32_t x0 = __float_as_uint(v[tk][e2].x), x1 = __float_as_uint(v[tk][e2].y);
-              const uint32_t h0 = x0 & 0xFFFFE000u, h1 = x1 & 0xFFFFE000u;
-              const float2 l = __ffma2_rn(f2(__uint_as_float(h0), __uint_as_float(h1)), f2(-1.f, -1.f), v[tk][e2]);
-              ah[tk][2 * e2] = h0; ah[tk][2 * e2 + 1] = h1;
-              al[tk][2 * e2] = __float_as_uint(l.x); al[tk][2 * e2 + 1] = __float_as_uint(l.y);
-            }
-#pragma unroll
-          for (int t = 0; t < 2; ++t) {
-            const uint32_t b0 = qh[s][2 * t], b1 = qh[s][2 * t + 1];
-            mma_tf32_1688(s_h, ah[0][2 * t], ah[1][2 * t], ah[0][2 * t + 1], ah[1][2 * t + 1], b0, b1);
-            mma_tf32_1688(s_l, al[0][2 * t], al[1][2 * t], al[0][2 * t + 1], al[1][2 * t + 1], b0, b1);
-            if (!PACK)
-              mma_tf32_1688(s_x, ah[0][2 * t], ah[1][2 * t], ah[0][2 * t + 1], ah[1][2 * t + 1],
-                            ql[PACK ? 0 : s][PACK ? 0 : 2 * t], ql[PACK ? 0 : s][PACK ? 0 : 2 * t + 1]);
+          for (int e2 = 0; e2 < 2; ++e2) {
+            const uint32_t x0 = __float_as_uint(v[tk][e2].x), x1 = __float_as_uint(v[tk][e2].y);
+            const uint32_t h0 = x0 & 0xFFFF0000u, h1 = x1 & 0xFFFF0000u;
+            const float2 l = __ffma2_rn(f2(__uint_as_float(h0), __uint_as_float(h1)), f2(-1.f, -1.f), v[tk][e2]);
+            ah[tk + 2 * e2] = __byte_perm(x0, x1, 0x7632);
+            al[tk + 2 * e2] = __byte_perm(__float_as_uint(l.x), __float_as_uint(l.y), 0x7632);
           }
-        } else {
-          uint32_t ah[4], al[4];
-#pragma unroll
-          for (int tk = 0; tk < 2; ++tk)
-#pragma unroll
-            for (int e2 = 0; e2 < 2; ++e2) {
-              const uint32_t x0 = __float_as_uint(v[tk][e2].x), x1 = __float_as_uint(v[tk][e2].y);
-              const uint32_t h0 = x0 & 0xFFFF0000u, h1 = x1 & 0xFFFF0000u;
-              const float2 l = __ffma2_rn(f2(__uint_as_float(h0), __uint_as_float(h1)), f2(-1.f, -1.f), v[tk][e2]);
-              ah[tk + 2 * e2] = __byte_perm(x0, x1, 0x7632);
-              al[tk + 2 * e2] = __byte_perm(__float_as_uint(l.x), __float_as_uint(l.y), 0x7632);
-            }
-          mma_bf16_16816(s_h, ah, qh[s][0], qh[s][1]);
-          mma_bf16_16816(s_l, al, qh[s][0], qh[s][1]);
-          if (!PACK) mma_bf16_16816(s_x, ah, ql[PACK ? 0 : s][0], ql[PACK ? 0 : s][PACK ? 0 : 1]);
-        }
+        mma_bf16_16816(s_h, ah, qh[s][0], qh[s][1]);
+        mma_bf16_16816(s_l, al, qh[s][0], qh[s][1]);
+        if (!PACK) mma_bf16_16816(s_x, ah, ql[PACK ? 0 : s][0], ql[PACK ? 0 : s][1]);
       };
-      auto do_chunk = [&](int i) {
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
         float2 lo[2][2], hi[2][2];
 #pragma unroll
         for (int tk = 0; tk < 2; ++tk) {
-          const float4 x = lds128(row_lo[tk] + coff[i]);
-          const float4 y = lds128(row_hi[tk] + coff[i]);
+          const float4 x = lds128(row_lo[tk] ^ (uint32_t)(i * 16));
+          const float4 y = lds128(row_hi[tk] ^ (uint32_t)(i * 16));
           const float2 rl = f2(rad_lo[tk], rad_lo[tk]), rh = f2(rad_hi[tk], rad_hi[tk]);
           const float2 x0 = __fmul2_rn(f2(x.x, x.y), rl), x1 = __fmul2_rn(f2(x.z, x.w), rl);
           const float2 y0 = __fmul2_rn(f2(y.x, y.y), rh), y1 = __fmul2_rn(f2(y.z, y.w), rh);
           if constexpr (ROT) {
-            float4 c, sn;
-            if constexpr (STAGED) {
-              const uint32_t ad = cs_lane + tk * 8 * CS_PITCH + (i / NH) * CS_HALF + (i % NH) * 128;
-              c = lds128(ad);
-              sn = lds128(ad + 16);
-            } else {
-              c = cs[STAGED ? 0 : tk][STAGED ? 0 : i][0];
-              sn = cs[STAGED ? 0 : tk][STAGED ? 0 : i][1];
-            }
+            const float4 c = cs[tk][i][0], sn = cs[tk][i][1];
             const float2 c0 = f2(c.x, c.y), c1 = f2(c.z, c.w);
             const float2 s0 = f2(sn.x, sn.y), s1 = f2(sn.z, sn.w);
-            const float2 n0 = f2(-sn.x, -sn.y), n1 = f2(-sn.z, -sn.w);
-            lo[tk][0] = __ffma2_rn(y0, n0, __fmul2_rn(x0, c0));
-            lo[tk][1] = __ffma2_rn(y1, n1, __fmul2_rn(x1, c1));
+            // x cos - y sin needs a negated operand and the packed fma has no negate modifier: the
+            // negative radius gives -y for the price of two packed multiplies
+            const float2 rn = f2(-rad_hi[tk], -rad_hi[tk]);
+            const float2 m0 = __fmul2_rn(f2(y.x, y.y), rn), m1 = __fmul2_rn(f2(y.z, y.w), rn);
+            lo[tk][0] = __ffma2_rn(m0, s0, __fmul2_rn(x0, c0));
+            lo[tk][1] = __ffma2_rn(m1, s1, __fmul2_rn(x1, c1));
             hi[tk][0] = __ffma2_rn(x0, s0, __fmul2_rn(y0, c0));
             hi[tk][1] = __ffma2_rn(x1, s1, __fmul2_rn(y1, c1));
           } else {
@@ -809,98 +855,86 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         }
         qk_chunk(i, lo);
         qk_chunk(NCH + i, hi);
-      };
-
-      ok_wait &= wait_cs_half(0);
-      if (live) {
-#pragma unroll
-        for (int i = 0; i < NH; ++i) do_chunk(i);
       }
-      __syncwarp();
-      if (k + 1 < nt) issue_cs_half(0, nx1.pos);
-      ok_wait &= wait_cs_half(1);
-      if (live) {
-#pragma unroll
-        for (int i = NH; i < NCH; ++i) do_chunk(i);
-      }
-      __syncwarp();
-      if (k + 1 < nt) { issue_cs_half(1, nx1.pos); issue_cs_regs(nx1.pos); }
+      // the cos/sin registers are free: fetch the next tile's rows
+      if (k + 1 < nt) issue_cs(pos_n);
 
-      float pv[4] = {0.f, 0.f, 0.f, 0.f};
-      if (live) {
-        // ---- online softmax over the 16 token rows, per head column ------------------
-        float sv[4];
+      // ---- online softmax over the 16 token rows, per head column ------------------
+      float sv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sv[e] = s_h[e] + (s_l[e] + s_x[e]);
+        // packed columns: head h's logit = column h (x q_hi) + column 4+h (x q_lo)
+        if (PACK) sv[e] += __shfl_xor_sync(0xffffffffu, sv[e], 2);
+      }
+      if (EXTRA && p.logits_out != nullptr) {
+        const int lb = tile_lb(k);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          sv[e] = s_h[e] + (s_l[e] + s_x[e]);
-          // packed columns: head h's logit = column h (x q_hi) + column 4+h (x q_lo)
-          if (PACK) sv[e] += __shfl_xor_sync(0xffffffffu, sv[e], 2);
+          const int n = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
+          if (n < a.grp && tok < cnt_tile && (!PACK || j < 2))
+            p.logits_out[(((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + lb) * N +
+                         16 * sub + tok] = sv[e] * kLn2;
         }
-        if (EXTRA && p.logits_out != nullptr) {
-          const int lb = tile_lb(k);
+      }
+      // rows without a token (past the page's count, or position -1) take no part; whatever
+      // their stale page bytes produced above is replaced here
+      const bool ok0 = r < cnt_tile && (!ROT || pos_c[0] >= 0);
+      const bool ok1 = (r + 8) < cnt_tile && (!ROT || pos_c[1] >= 0);
+      if (!ok0) sv[0] = sv[1] = -INFINITY;
+      if (!ok1) sv[2] = sv[3] = -INFINITY;
+      float tmax[2] = {fmaxf(sv[0], sv[2]), fmaxf(sv[1], sv[3])};
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = 2 * j + (e & 1), tok = r + ((e >> 1) << 3);
-            if (n < a.grp && tok < cnt_tile && (!PACK || j < 2))
-              p.logits_out[(((int64_t)b * p.Hq + (int64_t)hkv * a.grp + n) * p.max_blocks + lb) * N +
-                           16 * sub + tok] = sv[e] * kLn2;
-          }
+      for (int o = 4; o < 32; o <<= 1) {
+        tmax[0] = fmaxf(tmax[0], __shfl_xor_sync(0xffffffffu, tmax[0], o));
+        tmax[1] = fmaxf(tmax[1], __shfl_xor_sync(0xffffffffu, tmax[1], o));
+      }
+      float alpha[2], msafe[2], pv[4];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float mn = fmaxf(m_run[c], tmax[c]);
+        msafe[c] = (mn == -INFINITY) ? 0.f : mn;
+        alpha[c] = fast_exp2(m_run[c] - msafe[c]);
+        m_run[c] = mn;
+      }
+      pv[0] = fast_exp2(sv[0] - msafe[0]);
+      pv[1] = fast_exp2(sv[1] - msafe[1]);
+      pv[2] = fast_exp2(sv[2] - msafe[0]);
+      pv[3] = fast_exp2(sv[3] - msafe[1]);
+      l_run[0] = l_run[0] * alpha[0] + (pv[0] + pv[2]);
+      l_run[1] = l_run[1] * alpha[1] + (pv[1] + pv[3]);
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int dt = 0; dt < KS; ++dt) {
+          acc[dt][0] *= alpha[0]; acc[dt][1] *= alpha[1];
+          acc[dt][2] *= alpha[0]; acc[dt][3] *= alpha[1];
         }
-        const bool ok0 = r < cnt_tile && (!ROT || cur.pos[0] >= 0);
-        const bool ok1 = (r + 8) < cnt_tile && (!ROT || cur.pos[1] >= 0);
-        if (!ok0) sv[0] = sv[1] = -INFINITY;
-        if (!ok1) sv[2] = sv[3] = -INFINITY;
-        float tmax[2] = {fmaxf(sv[0], sv[2]), fmaxf(sv[1], sv[3])};
+      }
+      if (EXTRA && ml_seg != nullptr) {
+        // per-tile (max, sum) in the natural-log domain for heads 2j, 2j+1
+        float ls[2] = {pv[0] + pv[2], pv[1] + pv[3]};
 #pragma unroll
         for (int o = 4; o < 32; o <<= 1) {
-          tmax[0] = fmaxf(tmax[0], __shfl_xor_sync(0xffffffffu, tmax[0], o));
-          tmax[1] = fmaxf(tmax[1], __shfl_xor_sync(0xffffffffu, tmax[1], o));
+          ls[0] += __shfl_xor_sync(0xffffffffu, ls[0], o);
+          ls[1] += __shfl_xor_sync(0xffffffffu, ls[1], o);
         }
-        float alpha[2], msafe[2];
+        if (r == 0) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const float mn = fmaxf(m_run[c], tmax[c]);
-          msafe[c] = (mn == -INFINITY) ? 0.f : mn;
-          alpha[c] = fast_exp2(m_run[c] - msafe[c]);
-          m_run[c] = mn;
-        }
-        pv[0] = fast_exp2(sv[0] - msafe[0]);
-        pv[1] = fast_exp2(sv[1] - msafe[1]);
-        pv[2] = fast_exp2(sv[2] - msafe[0]);
-        pv[3] = fast_exp2(sv[3] - msafe[1]);
-        l_run[0] = l_run[0] * alpha[0] + (pv[0] + pv[2]);
-        l_run[1] = l_run[1] * alpha[1] + (pv[1] + pv[3]);
-        if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
-#pragma unroll
-          for (int dt = 0; dt < KS; ++dt) {
-            acc[dt][0] *= alpha[0]; acc[dt][1] *= alpha[1];
-            acc[dt][2] *= alpha[0]; acc[dt][3] *= alpha[1];
-          }
-        }
-        if (EXTRA && ml_seg != nullptr) {
-          // per-tile (max, sum) in the natural-log domain for heads 2j, 2j+1
-          float ls[2] = {pv[0] + pv[2], pv[1] + pv[3]};
-#pragma unroll
-          for (int o = 4; o < 32; o <<= 1) {
-            ls[0] += __shfl_xor_sync(0xffffffffu, ls[0], o);
-            ls[1] += __shfl_xor_sync(0xffffffffu, ls[1], o);
-          }
-          if (r == 0) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              const int n = 2 * j + c;
-              if (n < a.grp && (!PACK || j < 2)) {
-                float* dst = ml_seg + n * ml_head + 2 * kWarps * k;
-                const float tm = tmax[c];
-                dst[0] = tm * kLn2;
-                dst[1] = (tm == -INFINITY) ? 0.f : ls[c] * fast_exp2(msafe[c] - tm);
-              }
+          for (int c = 0; c < 2; ++c) {
+            const int n = 2 * j + c;
+            if (n < a.grp && (!PACK || j < 2)) {
+              float* dst = ml_seg + n * ml_head + 2 * kWarps * k;
+              const float tm = tmax[c];
+              dst[0] = tm * kLn2;
+              dst[1] = (tm == -INFINITY) ? 0.f : ls[c] * fast_exp2(msafe[c] - tm);
             }
           }
         }
+      }
 
-        // ---- P^T through shared memory into the B-operand layout -------------------
-        // pbuf[h][head][token]: fp16 (or bf16 hi / lo for a bf16 V pool)
+      // ---- P^T through shared memory into the B-operand layout -------------------
+      // pbuf[h][head][token]: fp16 (or bf16 hi / lo for a bf16 V pool)
+      {
         uint16_t* ph = pbuf;
         uint16_t* pl = pbuf + 8 * 16;
 #pragma unroll
@@ -923,15 +957,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
             if (kBf16) pl[head * 16 + tok] = lbits;
           }
         }
-      } else if (EXTRA && ml_seg != nullptr && lane < a.grp) {  // a tile without tokens: (-inf, 0)
-        float* dst = ml_seg + lane * ml_head + 2 * kWarps * k;
-        dst[0] = -INFINITY;
-        dst[1] = 0.f;
       }
       uint32_t v_stage;
-      ok_wait &= wait_v(v_stage);  // tile k's V has landed
+      const bool v_ok = wait_v(v_stage);  // tile k's V has landed
       __syncwarp();
-      if (live) {
+      {
         const uint32_t* ph32 = reinterpret_cast<const uint32_t*>(pbuf);
         const uint32_t b0 = ph32[(r * 16 + 2 * j) >> 1];
         const uint32_t b1 = ph32[(r * 16 + 2 * j + 8) >> 1];
@@ -942,13 +972,10 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         }
         // ---- acc^T[dh][head] += V^T[dh][token] P^T[token][head] ---------------------
         const uint32_t vbase = smem_u32(v_ring) + v_stage * V_TILE;
-        const int mi = lane >> 3;
-        const int tau = (lane & 7) + ((mi >> 1) << 3);
 #pragma unroll
         for (int dt = 0; dt < KS; ++dt) {
-          const int c = 2 * dt + (mi & 1);
           uint32_t af[4];
-          ldmatrix_x4_trans(af, vbase + (c >> 3) * 2048 + tau * 128 + (((c & 7) ^ (tau & 7)) << 4));
+          ldmatrix_x4_trans(af, vbase + ldsm_off[dt & 3] + (dt >> 2) * 2048);
           if (kBf16) {
             mma_bf16_16816(acc[dt], af, b0, b1);
             if (!PACK) mma_bf16_16816(acc[dt], af, c0, c1);
@@ -958,20 +985,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         }
       }
       __syncwarp();
-      if (!__all_sync(0xffffffffu, ok_wait)) {
-        // an async copy never completed: flag it and stop; the partial row of this segment is
-        // not meaningful and the host sees the status bit
-        if (lane == 0 && p.status) atomicOr(p.status, SPHKV_ST_TIMEOUT);
-        dead = true;
-        return false;
-      }
-      return true;
-    };
-    for (int k = 0; k < nt; k += 3) {
-      if (!tile_step(k, kw_a, kw_b, kw_c)) break;
-      if (k + 1 < nt && !tile_step(k + 1, kw_b, kw_c, kw_a)) break;
-      if (k + 2 < nt && !tile_step(k + 2, kw_c, kw_a, kw_b)) break;
+      if (!__all_sync(0xffffffffu, v_ok)) { dead = true; break; }
     }
+    if (dead && lane == 0 && p.status) {
+      // an async copy never completed within the bounded wait: the partial row of this segment
+      // is not meaningful and the host sees the status bit
+      atomicOr(p.status, SPHKV_ST_TIMEOUT);
+    }
+    cp_async_wait<0>();  // the tail groups are empty; nothing of this segment stays in flight
+    k_read = k_issue;
 
     // ---- merge the warps of this CTA and write one partial row ---------------------
 #pragma unroll
@@ -1203,7 +1225,7 @@ static int smem_cb_layout(const sphkv_tiers& t, int dh, int budget_bytes, int* o
   int off = 0;
   for (int s = 0; s < t.n_slots; ++s) {
     const int bytes = dh * (1 << t.bits[s]) * 4;
-    const bool want = t.g[s] == 16 && (SPHKV_CB_DUP == 2 || (SPHKV_CB_DUP == 1 && t.bits[s] <= 4));
+    const bool want = t.g[s] == 16;
     dup[s] = (want && bytes <= extra_left) ? 1 : 0;
     if (dup[s]) extra_left -= bytes;
     offs[s] = off;
@@ -1266,10 +1288,10 @@ static int make_v_map(CUtensorMap* map, const sphkv_decode_params& p) {
   return 0;
 }
 
-template <int DH, typename VT, bool ROT, bool EXTRA, bool PACK>
+template <int DH, typename VT, bool ROT, int MODE, bool PACK>
 static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   static SmemOptIn opt_in;
-  auto kern = decode_splitk_kernel<DH, VT, ROT, EXTRA, PACK>;
+  auto kern = decode_splitk_kernel<DH, VT, ROT, MODE, PACK>;
   if (int rc = ensure_dynamic_smem(opt_in, (const void*)kern, smem_bytes, "decode")) return rc;
   kern<<<a.n_ctas, kWarps * 32, smem_bytes, st>>>(a);
   return check_launch("decode_splitk_kernel");
@@ -1279,10 +1301,13 @@ template <int DH, typename VT, bool ROT>
 static int launch_decode_r(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   const bool extra = a.p.logits_out != nullptr || a.p.page_ml != nullptr;
   const bool pack = a.grp <= 4;
-  if (extra) return pack ? launch_decode_t<DH, VT, ROT, true, true>(a, smem_bytes, st)
-                         : launch_decode_t<DH, VT, ROT, true, false>(a, smem_bytes, st);
-  return pack ? launch_decode_t<DH, VT, ROT, false, true>(a, smem_bytes, st)
-              : launch_decode_t<DH, VT, ROT, false, false>(a, smem_bytes, st);
+  if (extra) return pack ? launch_decode_t<DH, VT, ROT, 2, true>(a, smem_bytes, st)
+                         : launch_decode_t<DH, VT, ROT, 2, false>(a, smem_bytes, st);
+  if (a.p.page_size == 16 && a.p.radius_fmt == SPHKV_RADIUS_I8)
+    return pack ? launch_decode_t<DH, VT, ROT, 0, true>(a, smem_bytes, st)
+                : launch_decode_t<DH, VT, ROT, 0, false>(a, smem_bytes, st);
+  return pack ? launch_decode_t<DH, VT, ROT, 1, true>(a, smem_bytes, st)
+              : launch_decode_t<DH, VT, ROT, 1, false>(a, smem_bytes, st);
 }
 
 template <int DH, typename VT>
@@ -1300,7 +1325,7 @@ extern "C" int sphkv_rope_table_build(float* table, int32_t max_pos, int32_t dh,
   SPHKV_REQUIRE(table && inv_freq, SPHKV_E_ARG, "rope_table: NULL pointer");
   SPHKV_REQUIRE(max_pos > 0 && (dh == 64 || dh == 128), SPHKV_E_ARG, "rope_table: max_pos=%d dh=%d",
                 max_pos, dh);
-  SPHKV_REQUIRE(((uintptr_t)table & 15) == 0, SPHKV_E_ALIGN, "rope_table: table needs 16 B");
+  SPHKV_REQUIRE(((uintptr_t)table & 31) == 0, SPHKV_E_ALIGN, "rope_table: table needs 32-byte alignment");
   const int64_t n = (int64_t)max_pos * (dh / 2);
   rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       table, max_pos, dh, inv_freq);
@@ -1347,9 +1372,9 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
                 "decode: radius_fmt=%d", p.radius_fmt);
   SPHKV_REQUIRE(((uintptr_t)p.v_pool & 15) == 0 && ((uintptr_t)p.k_pages & 3) == 0 &&
                     ((uintptr_t)p.codebooks & 15) == 0 && (p.tiers.g_max & 3) == 0 &&
-                    (p.rope_table == nullptr || ((uintptr_t)p.rope_table & 15) == 0) &&
+                    (p.rope_table == nullptr || ((uintptr_t)p.rope_table & 31) == 0) &&
                     ((uintptr_t)p.scratch & 255) == 0,
-                SPHKV_E_ALIGN, "decode: v_pool/rope_table/codebooks need 16 B, k_pages 4 B, scratch 256 B");
+                SPHKV_E_ALIGN, "decode: v_pool/codebooks need 16 B, rope_table 32 B, k_pages 4 B, scratch 256 B");
   if (int rc = validate_tiers(p.tiers, p.dh)) return rc;
 
   DecodeArgs a;
@@ -1365,7 +1390,7 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
   a.rows = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p.scratch) +
                                     align_up((int64_t)(a.n_units + 1) * 4, 256));
   a.plan_in_kernel = a.n_units <= kMaxUnitsInKernelPlan ? 1 : 0;
-  const int fixed_bytes = smem_v_bytes(p.dh) + (p.rope_table ? smem_cs_bytes(p.dh) : smem_cs_bytes(p.dh)) +
+  const int fixed_bytes = smem_v_bytes(p.dh) + 
                           kWarps * smem_priv_bytes() + (a.plan_in_kernel ? (a.n_units + 1) * 4 : 0);
   a.cb_smem_bytes = smem_cb_layout(p.tiers, p.dh, 227 * 1024 - fixed_bytes, a.cb_smem_off, a.cb_dup);
   const int smem_bytes = fixed_bytes + a.cb_smem_bytes;
