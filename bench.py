@@ -153,14 +153,34 @@ class CpuReference:
         self.total_units = CFG["B"] * Hkv
         self.desc = (f"{n_units} of {self.total_units} (batch row, KV head) units at ctx {ctx} per step, "
                      f"scaled linearly to the full layer-step")
+        self.K, self.V, self.cbs, self.assign, self.specs = K, V, cbs, assign, specs
+        self.last_out = None
+
+    def gpu_same_input_diff(self, dev) -> float:
+        """The units this arm evaluates, decoded by the CUDA path from the same seeded keys, values,
+        queries and codebooks (uploaded bits): max-abs difference of the attention outputs."""
+        pkg = importlib.import_module("spherical-kv_b200")
+        dh, ctx = CFG["dh"], CFG["ctx"]
+        tiers = pkg.TierSet(dh, self.specs)
+        lists = pkg.build_page_lists(self.assign.to(dev), tiers, CFG["page_size"], shuffle_seed=0)
+        cache = pkg.encode_pages(self.K[0].to(dev), self.V[0].to(dev), lists,
+                                 tiers.pack_codebooks(self.cbs).to(dev), tiers)
+        rope = pkg.rope_table(ctx + 8, dh, device=dev)
+        out = pkg.decode_paged(self.Q.to(dev), cache, rope).float().cpu()[0]
+        if self.last_out is None:
+            self.step_us()
+        return float((out - self.last_out).abs().max())
 
     def step_us(self) -> float:
         """One pass over the sample; microseconds per full layer-step (scaled)."""
         t0 = time.perf_counter()
+        outs = []
         for h, tl in enumerate(self.units):
-            self.orc.decode_unit(self.Q[0, h * self.grp:(h + 1) * self.grp], tl, self.cos, self.sin,
-                                 torch.float32)
-        return (time.perf_counter() - t0) / self.n_units * self.total_units * 1e6
+            outs.append(self.orc.decode_unit(self.Q[0, h * self.grp:(h + 1) * self.grp], tl, self.cos, self.sin,
+                                             torch.float32)[1])
+        dt = time.perf_counter() - t0
+        self.last_out = torch.cat(outs, 0)
+        return dt / self.n_units * self.total_units * 1e6
 
 
 def run_reference(args) -> None:
@@ -478,6 +498,156 @@ def run_side_workload(args) -> None:
         dist.destroy_process_group()
 
 
+
+def _graph_time(fn, steps, warmup, dev, world):
+    """Records `fn` into a CUDA graph on a side stream, replays it `steps` times between events;
+    milliseconds per replay, max over ranks."""
+    import torch.distributed as dist
+    st = torch.cuda.Stream(device=dev)
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        fn(); fn()
+        st.synchronize()
+        if world > 1:
+            dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            fn()
+        for _ in range(warmup):
+            g.replay()
+        st.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(steps):
+            g.replay()
+        e1.record(st)
+        st.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+    torch.cuda.current_stream().wait_stream(st)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def splitkv_block(args, pkg, dev, rank, world):
+    """BASELINE config 5 on the ranks of this run: one 131072-token sequence (batch 1, 20/60/20),
+    its pages cut contiguously over the GPUs, partial (max, sum, acc) rows exchanged by peer stores
+    inside the merge kernel.  T1 is measured in the same run (every rank decodes the whole sequence
+    alone, same launch mode), so the efficiency T1 / (n * Tn) compares like with like."""
+    Hq, Hkv, dh, N = CFG["Hq"], CFG["Hkv"], CFG["dh"], CFG["page_size"]
+    ctx, n_seq = 131072, 4   # distinct sequences cycled: a step never finds its pages in L2
+    specs = pkg.REFERENCE_TIERS[:2]
+    tiers = pkg.TierSet(dh, specs)
+    gen = torch.Generator(device=dev).manual_seed(4242)   # the same sequences on every rank
+    scale = torch.exp(0.5 * torch.randn(dh, generator=gen, device=dev))
+    rope = pkg.rope_table(ctx + 8, dh, device=dev)
+    fulls, shards, qs, alg = [], [], [], None
+    for i in range(n_seq):
+        assign = pkg.synth.make_tier_assign(1, Hkv, ctx, {1: 0.2, 2: 0.6}, seed=500 + i).to(dev)
+        lists = pkg.build_page_lists(assign, tiers, N, shuffle_seed=i)
+        K = (torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+        V = (torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale).bfloat16()
+        cb = tiers.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs, seed=i)])
+        cache = pkg.encode_pages(K, V, lists, cb, tiers, v_dtype=torch.bfloat16)
+        fulls.append(cache)
+        shards.append(pkg.split_kv.shard_cache(cache, rank, world))
+        qs.append((torch.randn(1, Hq, dh, generator=gen, device=dev) * scale).bfloat16())
+        if alg is None:
+            alg = algorithmic_bytes(lists, tiers, dh) - CFG["B"] * Hq * dh * 4 + Hq * dh * 4
+        del K, V
+    out_full = [torch.empty(1, Hq, dh, dtype=torch.bfloat16, device=dev) for _ in range(n_seq)]
+    out_split = [torch.empty(1, Hq, dh, dtype=torch.bfloat16, device=dev) for _ in range(n_seq)]
+
+    def full_step():
+        for c, q, o in zip(fulls, qs, out_full):
+            pkg.decode_paged(q, c, rope, out=o)
+
+    t1_us = _graph_time(full_step, args.steps, args.warmup, dev, world) * 1e3 / n_seq
+    blk = {"workload": f"split-KV decode, B1 Hq{Hq} Hkv{Hkv} dh{dh} ctx {ctx}, 20/60/20, pages cut contiguously "
+                       f"over {world} GPU(s); {n_seq} sequences cycled (inputs larger than L2); CUDA-graph replay",
+           "n_gpus": world, "t1_us_per_step": t1_us, "algorithmic_bytes": alg,
+           "t1_hbm_gbs": alg / (t1_us * 1e-6) / 1e9}
+    if world == 1:
+        blk.update({"us_per_step": t1_us, "efficiency": 1.0, "exchange": "none (one GPU)"})
+        return blk
+    ex = pkg.split_kv.PeerExchange(1, Hq, Hkv, dh, device=dev)
+
+    def split_step():
+        for c, q, o in zip(shards, qs, out_split):
+            pkg.decode_paged(q, c, rope, out=o, exchange=ex)
+
+    tn_us = _graph_time(split_step, args.steps, args.warmup, dev, world) * 1e3 / n_seq
+    torch.cuda.synchronize()
+    diff = max(float((a.float() - b.float()).abs().max()) for a, b in zip(out_split, out_full))
+    status = sum(int(c.status.item()) for c in shards)
+    st = torch.tensor([diff, float(status)], device=dev)
+    import torch.distributed as dist
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    blk.update({"us_per_step": tn_us, "efficiency": t1_us / (world * tn_us),
+                "exchange": "peer stores + sequence flags + bounded wait inside the merge kernel (no collective)",
+                "bytes_sent_per_rank_per_step": (world - 1) * Hq * (dh + 2) * 4,
+                "merged_vs_single_pass_max_abs": float(st[0].item()), "kernel_status": int(st[1].item()),
+                "achieved_hbm_gbs_all_gpus": alg / (tn_us * 1e-6) / 1e9})
+    return blk
+
+
+def encode_c4_block(args, pkg, dev):
+    """BASELINE config 4 shape, a few layers at a time: 32768 tokens x 8 KV heads x dh 128 of fp32
+    keys with 1 % of the channels scaled by 20; every token-head gets its tier-1 and its tier-2 codes
+    from ONE pass over the keys, then both sets of bit-packed pages are assembled from the codes."""
+    Hkv, dh, N, ctx, layers = CFG["Hkv"], CFG["dh"], CFG["page_size"], 32768, 4
+    specs = pkg.REFERENCE_TIERS[:2]
+    tiers = pkg.TierSet(dh, specs)
+    gen = torch.Generator(device=dev).manual_seed(99)
+    scale = torch.exp(0.5 * torch.randn(dh, generator=gen, device=dev))
+    scale[torch.randperm(dh, generator=torch.Generator().manual_seed(3))[:max(1, dh // 100)].to(dev)] *= 20
+    Ks = [torch.randn(ctx, Hkv, dh, generator=gen, device=dev) * scale for _ in range(layers)]
+    cb = tiers.pack_codebooks([c.to(dev) for c in pkg.synth.make_codebooks(Hkv, dh, specs, seed=9)])
+    l1 = pkg.build_page_lists(torch.full((1, Hkv, ctx), 1, dtype=torch.uint8, device=dev), tiers, N)
+    l2 = pkg.build_page_lists(torch.full((1, Hkv, ctx), 2, dtype=torch.uint8, device=dev), tiers, N)
+    codes = pkg.encode_codes(Ks[0], cb, tiers)
+    c1 = pkg.pages_from_codes(codes, None, l1, cb)
+    c2 = pkg.pages_from_codes(codes, None, l2, cb)
+    # bit-exactness of this route at this shape: the pages equal a direct encode of the keys
+    d1 = pkg.encode_pages(Ks[0], None, l1, cb, tiers)
+    d2 = pkg.encode_pages(Ks[0], None, l2, cb, tiers)
+    same = bool(torch.equal(c1.k_pages, d1.k_pages) and torch.equal(c2.k_pages, d2.k_pages))
+
+    def step():
+        for Kt in Ks:
+            cd = pkg.encode_codes(Kt, cb, tiers)
+            pkg.pages_from_codes(cd, None, l1, cb, out=c1)
+            pkg.pages_from_codes(cd, None, l2, cb, out=c2)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    th = layers * ctx * Hkv
+    macs = th * dh * (64 + 16)
+    fma_peak = 148 * 128 * 1.965e9   # fp32 FMA lanes x max SM clock
+    rd = th * dh * 4
+    wr = layers * (l1.pool_bytes + l2.pool_bytes)
+    return {"workload": f"{ctx} tokens x {layers} layers x {Hkv} KV heads x dh {dh}, fp32 keys with 1% x20 outlier "
+                        f"channels; tier-1 (64 centroids) and tier-2 (16) codes in one pass over the keys, both page sets "
+                        f"assembled from the codes ({N}-token pages)",
+            "ms_per_32_layers": ms / layers * 32, "token_heads_per_s": th / (ms * 1e-3),
+            "tmac_per_s": macs / (ms * 1e-3) / 1e12, "frac_of_fma_peak": macs / (ms * 1e-3) / fma_peak,
+            "hbm_gbs": (rd + wr) / (ms * 1e-3) / 1e9, "pages_identical_to_direct_encode": same}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -489,6 +659,7 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=CFG["ctx"])
     ap.add_argument("--batch", type=int, default=CFG["B"], help="batch rows per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the split-KV and encode blocks of the line")
     ap.add_argument("--ema", action="store_true",
                     help="also update the page-importance EMA in the decode epilogue (per-tile statistics + "
                          "omega blend inside the merge kernel); off for the headline line")
@@ -662,7 +833,22 @@ def main() -> None:
             ref.step_us()
             v = min(ref.step_us() for _ in range(3))
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": ref.desc + ", best of 3"}
+                                    "sample": ref.desc + ", best of 3",
+                                    "same_units_gpu_vs_cpu_max_abs": ref.gpu_same_input_diff(dev),
+                                    "same_units_note": "the CUDA path decoded the very units timed here (same seeded "
+                                                       "keys, values, queries, codebooks); it reads int8-radius pages, "
+                                                       "the reference torch path its raw fp32 radii"}
+    # ---- side measurements carried in the same line: split-KV (config 5) at this run's GPU count and
+    #      encode / page build (config 4); both after the headline timing, on every rank ----
+    del caches, graph
+    torch.cuda.empty_cache()
+    splitkv = None if args.no_side else splitkv_block(args, pkg, dev, rank, world)
+    encode_c4 = None if (args.no_side or rank != 0) else encode_c4_block(args, pkg, dev)
+    if rank == 0:
+        if splitkv is not None:
+            line["splitkv"] = splitkv
+        if encode_c4 is not None:
+            line["encode_c4"] = encode_c4
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SPHKV_ABI_VERSION 2
+#define SPHKV_ABI_VERSION 3
 
 /* error codes */
 #define SPHKV_OK 0
@@ -46,6 +46,7 @@ extern "C" {
 
 #define SPHKV_MAX_TIER_SLOTS 4
 #define SPHKV_MAX_GQA 8 /* query heads per KV head handled by one kernel pass        */
+#define SPHKV_MAX_XCHG_RANKS 16 /* GPUs one split-KV exchange can span                  */
 
 /* Geometry of the codebook tensor and of the tiers stored in it.  The codebook
  * tensor has the layout of LayerPool.cb_flat (sphkv_lut.py:108-111):
@@ -178,6 +179,29 @@ typedef struct sphkv_decode_params {
   float sm_scale;
   float ema_beta;             /* EMA factor for omega (the reference uses 0.9)        */
   sphkv_tiers tiers;
+  /* Cross-GPU split-KV exchange inside the merge kernel (xchg_world <= 1: off).  The block
+   * tables of this call cover this rank's share of every sequence; the un-normalised
+   * (max, sum, acc) rows of every (batch row, query head) are stored straight into every
+   * rank's receive buffer (plain peer stores over NVLink), a per-(rank, unit) sequence flag is
+   * released, and the same kernel waits -- bounded -- for the flags of all ranks, combines the
+   * `xchg_world` partial sets by log-sum-exp (math of decode_kernel.cu:230-245) and writes
+   * `out`.  No collective library call, no extra launch.
+   *   xchg_recv[q]  : rank q's receive buffer in rank q's memory, f32
+   *                   [2][xchg_world][B*Hq][dh+2] (two slots alternate by step)
+   *   xchg_flags[q] : rank q's flags, i32 [2][xchg_world][B*Hkv] (one set per slot),
+ *                   zero-initialised once
+   *   xchg_seq      : this rank's step counters, i32 [B*Hkv], zero-initialised once; every
+   *                   call advances them by one, so calls replay from a CUDA graph
+   * Both pointer arrays live in device memory of this rank and hold xchg_world entries (entry
+   * xchg_rank = this rank's own buffers).  All ranks must issue the same sequence of calls.  A
+   * wait that exceeds xchg_timeout_cycles SM clocks (0 = 2e9, about a second) gives up: the
+   * kernel raises SPHKV_ST_TIMEOUT in `status`, writes zeros to the rows it could not
+   * complete and returns. */
+  float* const* xchg_recv;
+  int32_t* const* xchg_flags;
+  int32_t* xchg_seq;
+  int64_t xchg_timeout_cycles;
+  int32_t xchg_rank, xchg_world;
 } sphkv_decode_params;
 
 #define SPHKV_ST_BAD_POSITION 1 /* a key position was outside [0, max_pos)            */

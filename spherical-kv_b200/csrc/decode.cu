@@ -612,20 +612,28 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
     // chunk's {cos x 4, sin x 4} (the table is L2 resident), issued for tile k + 1 once tile k
     // has used its own
     float4 cs[2][NCH][2];
-    auto issue_cs = [&](const int (&ps)[2]) {
+    const float4* cs_src[2] = {nullptr, nullptr};  // this lane's pieces of the two table rows
+    auto cs_rows = [&](const int (&ps)[2]) {
       if constexpr (ROT) {
 #pragma unroll
-        for (int tk = 0; tk < 2; ++tk) {
-          const float4* rp = reinterpret_cast<const float4*>(p.rope_table) + (clamp_pos(ps[tk]) * (DH / 4) + j * 2);
-#pragma unroll
-          for (int i = 0; i < NCH; ++i) {
-            asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                         : "=f"(cs[tk][i][0].x), "=f"(cs[tk][i][0].y), "=f"(cs[tk][i][0].z), "=f"(cs[tk][i][0].w),
-                           "=f"(cs[tk][i][1].x), "=f"(cs[tk][i][1].y), "=f"(cs[tk][i][1].z), "=f"(cs[tk][i][1].w)
-                         : "l"(rp + i * 8));
-          }
-        }
+        for (int tk = 0; tk < 2; ++tk)
+          cs_src[tk] = reinterpret_cast<const float4*>(p.rope_table) + (clamp_pos(ps[tk]) * (DH / 4) + j * 2);
       }
+    };
+    auto issue_cs_chunk = [&](int i) {
+      if constexpr (ROT) {
+#pragma unroll
+        for (int tk = 0; tk < 2; ++tk)
+          asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=f"(cs[tk][i][0].x), "=f"(cs[tk][i][0].y), "=f"(cs[tk][i][0].z), "=f"(cs[tk][i][0].w),
+                         "=f"(cs[tk][i][1].x), "=f"(cs[tk][i][1].y), "=f"(cs[tk][i][1].z), "=f"(cs[tk][i][1].w)
+                       : "l"(cs_src[tk] + i * 8));
+      }
+    };
+    auto issue_cs = [&](const int (&ps)[2]) {
+      cs_rows(ps);
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) issue_cs_chunk(i);
     };
 
     auto stage_codebooks = [&]() {
@@ -827,6 +835,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         mma_bf16_16816(s_l, al, qh[s][0], qh[s][1]);
         if (!PACK) mma_bf16_16816(s_x, ah, ql[PACK ? 0 : s][0], ql[PACK ? 0 : s][1]);
       };
+      const bool more = k + 1 < nt;
+      if (more) cs_rows(pos_n);
 #pragma unroll
       for (int i = 0; i < NCH; ++i) {
         float2 lo[2][2], hi[2][2];
@@ -853,11 +863,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
             lo[tk][0] = x0; lo[tk][1] = x1; hi[tk][0] = y0; hi[tk][1] = y1;
           }
         }
+        // this chunk's cos/sin registers are free: fetch the next tile's
+        if (more) issue_cs_chunk(i);
         qk_chunk(i, lo);
         qk_chunk(NCH + i, hi);
       }
-      // the cos/sin registers are free: fetch the next tile's rows
-      if (k + 1 < nt) issue_cs(pos_n);
 
       // ---- online softmax over the 16 token rows, per head column ------------------
       float sv[4];
@@ -1184,7 +1194,94 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
       }
       dst[2 + d] = o;
     }
-    if (p.out != nullptr) store_from_float(p.out, p.out_dtype, hq * DH + d, l > 0.f ? o / l : 0.f);
+    if (p.out != nullptr && p.xchg_world <= 1)
+      store_from_float(p.out, p.out_dtype, hq * DH + d, l > 0.f ? o / l : 0.f);
+  }
+  if (p.xchg_world <= 1) return;
+
+  // ---- split-KV exchange: this rank's rows of the unit go to every rank, then the unit is
+  //      combined over the ranks here.  Peer memory is touched by plain stores only.
+  __shared__ int s_seq, s_ok;
+  __shared__ float s_rm[SPHKV_MAX_XCHG_RANKS][8], s_rl[SPHKV_MAX_XCHG_RANKS][8];
+  const int unit = b * p.Hkv + hkv;
+  const int n_units = p.B * p.Hkv;
+  const int64_t n_rows = (int64_t)p.B * p.Hq;
+  if (threadIdx.x == 0) s_seq = p.xchg_seq[unit] + 1;
+  __syncthreads();
+  const int seq = s_seq;
+  const int64_t slot_base = (int64_t)(seq & 1) * p.xchg_world * n_rows;  // rows
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+    const int i = threadIdx.x + q * 256;
+    const int n = i / DH, d = i - n * DH;
+    if (n >= a.grp) continue;
+    const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
+    const int64_t off = (slot_base + (int64_t)p.xchg_rank * n_rows + hq) * (DH + 2);
+    for (int peer = 0; peer < p.xchg_world; ++peer) {
+      float* dst = p.xchg_recv[peer] + off;
+      if (d == 0) {
+        dst[0] = s_M[n] * kLn2;
+        dst[1] = s_L[n];
+      }
+      dst[2 + d] = o_acc[q];
+    }
+  }
+  __threadfence_system();  // the rows are visible system-wide before the flag is
+  __syncthreads();
+  if (threadIdx.x < p.xchg_world) {
+    int32_t* flag = p.xchg_flags[threadIdx.x] + ((int64_t)(seq & 1) * p.xchg_world + p.xchg_rank) * n_units + unit;
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
+  }
+  // bounded wait for every rank's flag of this unit and step
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < p.xchg_world) {
+    const int32_t* flag = p.xchg_flags[p.xchg_rank] + ((int64_t)(seq & 1) * p.xchg_world + threadIdx.x) * n_units + unit;
+    const long long limit = p.xchg_timeout_cycles > 0 ? p.xchg_timeout_cycles : 2000000000LL;
+    const long long t0 = clock64();
+    int seen;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+      if (seen == seq) break;  // the flag of this slot: a later step of the peer uses the other slot
+      if (clock64() - t0 > limit) { s_ok = 0; break; }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) p.xchg_seq[unit] = seq;
+  if (!s_ok) {
+    // a rank never published this step: report it and leave defined output
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, SPHKV_ST_TIMEOUT);
+    if (p.out != nullptr)
+      for (int i = threadIdx.x; i < a.grp * DH; i += blockDim.x)
+        store_from_float(p.out, p.out_dtype, ((int64_t)b * p.Hq + (int64_t)hkv * a.grp) * DH + i, 0.f);
+    return;
+  }
+  const float* mine = p.xchg_recv[p.xchg_rank] + slot_base * (DH + 2);
+  for (int i = threadIdx.x; i < p.xchg_world * a.grp; i += blockDim.x) {
+    const int rr = i / a.grp, n = i - rr * a.grp;
+    const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
+    const float* pr = mine + ((int64_t)rr * n_rows + hq) * (DH + 2);
+    // the rows were written by other GPUs: read them past L1, which is not coherent with them
+    const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
+    s_rm[rr][n] = pl > 0.f ? pm : -INFINITY;
+    s_rl[rr][n] = pl;
+  }
+  __syncthreads();
+  if (p.out == nullptr) return;
+  for (int i = threadIdx.x; i < a.grp * DH; i += blockDim.x) {
+    const int n = i / DH, d = i - n * DH;
+    const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
+    float M = -INFINITY;
+    for (int rr = 0; rr < p.xchg_world; ++rr) M = fmaxf(M, s_rm[rr][n]);
+    float l = 0.f, o = 0.f;
+    if (M != -INFINITY)
+      for (int rr = 0; rr < p.xchg_world; ++rr) {
+        if (s_rm[rr][n] == -INFINITY) continue;
+        const float w = __expf(s_rm[rr][n] - M);
+        l += s_rl[rr][n] * w;
+        o += __ldcg(mine + ((int64_t)rr * n_rows + hq) * (DH + 2) + 2 + d) * w;
+      }
+    store_from_float(p.out, p.out_dtype, hq * DH + d, l > 0.f ? o / l : 0.f);
   }
 }
 
@@ -1376,6 +1473,16 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
                     ((uintptr_t)p.scratch & 255) == 0,
                 SPHKV_E_ALIGN, "decode: v_pool/codebooks need 16 B, rope_table 32 B, k_pages 4 B, scratch 256 B");
   if (int rc = validate_tiers(p.tiers, p.dh)) return rc;
+  if (p.xchg_world > 1) {
+    SPHKV_REQUIRE(p.xchg_world <= SPHKV_MAX_XCHG_RANKS, SPHKV_E_LIMIT, "decode: xchg_world=%d (max %d)",
+                  p.xchg_world, SPHKV_MAX_XCHG_RANKS);
+    SPHKV_REQUIRE(p.xchg_rank >= 0 && p.xchg_rank < p.xchg_world, SPHKV_E_ARG, "decode: xchg_rank=%d of %d",
+                  p.xchg_rank, p.xchg_world);
+    SPHKV_REQUIRE(p.xchg_recv && p.xchg_flags && p.xchg_seq, SPHKV_E_ARG,
+                  "decode: the exchange needs xchg_recv, xchg_flags and xchg_seq");
+    SPHKV_REQUIRE(p.omega == nullptr, SPHKV_E_ARG,
+                  "decode: the page-importance update is per rank; run it without the exchange");
+  }
 
   DecodeArgs a;
   a.p = p;

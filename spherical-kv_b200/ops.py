@@ -175,7 +175,7 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
                  page_ml: Optional[torch.Tensor] = None, logits_out: Optional[torch.Tensor] = None,
                  n_ctas: int = 0,
                  want_out: bool = True, omega: Optional[torch.Tensor] = None,
-                 ema_beta: float = 0.9) -> torch.Tensor:
+                 ema_beta: float = 0.9, exchange=None) -> torch.Tensor:
     """One decode-attention step over the compressed cache.
 
     q: [B, Hq, dh] post-RoPE at the query position.  rope: table from rope_table() (None =
@@ -186,6 +186,9 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     spherical_kv_pipeline.py:952-987, updated in place inside the merge kernel from the
     per-tile statistics of this step; `page_ml` (f32 [B, Hq, max_blocks, page_size/16, 2]) is
     allocated when omega is given without it.
+    `exchange` (split_kv.PeerExchange) turns the call into one rank's part of a split-KV decode:
+    `cache` then holds this rank's share of every block list and the merge kernel trades the
+    partial rows with the other ranks over peer memory before it writes `out`.
     The split-K scratch and the status word live in `cache` (grown when a later call needs
     more): one cache must not be decoded on two streams at once.  The status word is not read
     here (that would synchronise); `check_status(cache)` does it.
@@ -225,6 +228,11 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     p.radius_fmt, p.n_ctas = cache.radius_fmt, n_ctas
     p.sm_scale = (1.0 / math.sqrt(dh)) if sm_scale is None else sm_scale
     p.tiers = cache.tiers.to_c()
+    if exchange is not None and exchange.world > 1:
+        exchange.check_shape(B, Hq, L.Hkv, dh)
+        p.xchg_recv, p.xchg_flags = exchange.recv_ptrs.data_ptr(), exchange.flag_ptrs.data_ptr()
+        p.xchg_seq, p.xchg_timeout_cycles = exchange.seq.data_ptr(), exchange.timeout_cycles
+        p.xchg_rank, p.xchg_world = exchange.rank, exchange.world
     _lib.check(lib.sphkv_decode_paged(C.byref(p), _stream()), "sphkv_decode_paged")
     return out
 

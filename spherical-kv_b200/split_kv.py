@@ -1,12 +1,19 @@
 """Split-KV decode across GPUs: one long sequence's block lists are cut into contiguous
-ranges, every rank runs the decode kernel over its range and exports the un-normalised
-(max, sum, acc) triple per (batch row, query head); one all-gather moves the triples
-(B*Hq*(dh+2) floats per rank) into local memory and the log-sum-exp merge kernel finishes on
-every rank.  The reference has no multi-GPU path; its single-GPU analogue is the per-page
-partial + sphkv_reduce_kernel (decode_kernel.cu:212-246).
+ranges, every rank runs the decode kernel over its range and produces the un-normalised
+(max, sum, acc) triple per (batch row, query head); the triples (B*Hq*(dh+2) floats per rank)
+are exchanged and merged by log-sum-exp on every rank.  The reference has no multi-GPU path;
+its single-GPU analogue is the per-page partial + sphkv_reduce_kernel (decode_kernel.cu:212-246).
 
-One process per GPU, torch.distributed for the exchange (NCCL on GPUs; the plumbing is
-backend-agnostic and is exercised with gloo on CPUs in the tests).
+Two exchanges, one process per GPU either way:
+
+* `PeerExchange` (GPUs of one node): the merge kernel itself stores this rank's rows into every
+  rank's receive buffer with plain peer stores over NVLink, releases a per-(rank, unit) sequence
+  flag and waits -- bounded -- for the other ranks' flags before it combines.  A decode step is
+  the two launches of a single-GPU step; nothing is sent through a collective library, and the
+  step replays from a CUDA graph (the sequence numbers live in device memory).  torch.distributed
+  is used once, at set-up, to swap the CUDA IPC handles of the buffers.
+* `SplitKVDecoder` without a PeerExchange: an all-gather (NCCL on GPUs, gloo on CPUs in the
+  tests) followed by the merge kernel; the portable path.
 """
 from __future__ import annotations
 
@@ -26,6 +33,92 @@ def shard_cache(cache: PagedCache, rank: int, world: int) -> PagedCache:
                       radius_fmt=cache.radius_fmt)
 
 
+class ExchangeState:
+    """Bookkeeping of the peer exchange that needs no GPU: which of the two receive slots a step
+    uses and where a rank's rows and flags sit.  Mirrors the index arithmetic of the merge
+    kernel so that it can be checked on CPUs."""
+
+    def __init__(self, rank: int, world: int, B: int, Hq: int, Hkv: int, dh: int):
+        if not 0 <= rank < world:
+            raise ValueError(f"rank {rank} of {world}")
+        self.rank, self.world, self.B, self.Hq, self.Hkv, self.dh = rank, world, B, Hq, Hkv, dh
+        self.rows, self.units = B * Hq, B * Hkv
+
+    @property
+    def recv_numel(self) -> int:
+        return 2 * self.world * self.rows * (self.dh + 2)
+
+    @property
+    def flags_numel(self) -> int:
+        return 2 * self.world * self.units
+
+    def slot(self, seq: int) -> int:
+        """Receive slot of step `seq` (steps count from 1): the two slots alternate, so a rank
+        that is one step ahead never overwrites rows another rank still reads."""
+        return seq & 1
+
+    def row_offset(self, seq: int, src_rank: int, row: int) -> int:
+        """Element offset in a receive buffer of row `row` written by `src_rank` in step `seq`."""
+        return ((self.slot(seq) * self.world + src_rank) * self.rows + row) * (self.dh + 2)
+
+    def flag_offset(self, seq: int, src_rank: int, unit: int) -> int:
+        """Element offset of the flag `src_rank` releases for `unit` in step `seq`: flags are per
+        slot like the rows, so a rank that is already in the next step does not disturb it."""
+        return (self.slot(seq) * self.world + src_rank) * self.units + unit
+
+    @staticmethod
+    def arrived(flag_value: int, seq: int) -> bool:
+        """Step `seq` of a peer is in when the flag of that step's slot holds exactly `seq`: a
+        rank that skipped the step never writes it."""
+        return flag_value == seq
+
+
+class PeerExchange(ExchangeState):
+    """Receive buffers, flags and step counters of one rank plus the peers' device pointers.
+
+    Every rank allocates its buffers, exports them through CUDA IPC (the handles travel once
+    through `group`), opens the others' and uploads the pointer arrays the kernel reads.  Peer
+    access needs GPUs of one node that can reach each other (NVLink / NVSwitch or PCIe P2P)."""
+
+    def __init__(self, B: int, Hq: int, Hkv: int, dh: int, group=None, device=None,
+                 timeout_cycles: int = 0):
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        super().__init__(rank, world, B, Hq, Hkv, dh)
+        dev = torch.device(device if device is not None else torch.cuda.current_device())
+        self.timeout_cycles = int(timeout_cycles)
+        self.recv = torch.zeros(self.recv_numel, dtype=torch.float32, device=dev)
+        self.flags = torch.zeros(self.flags_numel, dtype=torch.int32, device=dev)
+        self.seq = torch.zeros(self.units, dtype=torch.int32, device=dev)
+        self._peers = []  # keeps the opened peer storages alive
+        recv_ptrs, flag_ptrs = [0] * world, [0] * world
+        recv_ptrs[rank], flag_ptrs[rank] = self.recv.data_ptr(), self.flags.data_ptr()
+        if world > 1:
+            torch.cuda.synchronize(dev)
+            mine = (self.recv.untyped_storage()._share_cuda_(), self.flags.untyped_storage()._share_cuda_())
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=group)
+            for q, (h_recv, h_flags) in enumerate(handles):
+                if q == rank:
+                    continue
+                t_recv = self._open(h_recv, torch.float32, self.recv_numel)
+                t_flags = self._open(h_flags, torch.int32, self.flags_numel)
+                self._peers.append((t_recv, t_flags))
+                recv_ptrs[q], flag_ptrs[q] = t_recv.data_ptr(), t_flags.data_ptr()
+            dist.barrier(group=group)  # every rank has opened every buffer before anyone decodes
+        self.recv_ptrs = torch.tensor(recv_ptrs, dtype=torch.int64, device=dev)
+        self.flag_ptrs = torch.tensor(flag_ptrs, dtype=torch.int64, device=dev)
+
+    @staticmethod
+    def _open(handle, dtype, numel):
+        storage = torch.UntypedStorage._new_shared_cuda(*handle)
+        return torch.empty(0, dtype=dtype, device=storage.device).set_(storage, 0, (numel,))
+
+    def check_shape(self, B: int, Hq: int, Hkv: int, dh: int) -> None:
+        if (B, Hq, Hkv, dh) != (self.B, self.Hq, self.Hkv, self.dh):
+            raise ValueError("PeerExchange was sized for another (B, Hq, Hkv, dh)")
+
+
 class SplitKVDecoder:
     """decode(q) -> out [B, Hq, dh] with the context spread over the ranks of `group`.
 
@@ -35,8 +128,8 @@ class SplitKVDecoder:
 
     def __init__(self, local_cache: PagedCache, B: int, Hq: int, group=None,
                  decode_fn: Optional[Callable] = None, merge_fn: Optional[Callable] = None,
-                 device=None, out_dtype: torch.dtype = torch.float32):
-        self.cache, self.group = local_cache, group
+                 device=None, out_dtype: torch.dtype = torch.float32, exchange: Optional[PeerExchange] = None):
+        self.cache, self.group, self.exchange = local_cache, group, exchange
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         dev = device if device is not None else local_cache.k_pages.device
         dh = local_cache.dh
@@ -53,6 +146,10 @@ class SplitKVDecoder:
         ops.merge_partials(parts, out=out.view(parts.shape[1], -1))
 
     def decode(self, q: torch.Tensor, rope: Optional[torch.Tensor]) -> torch.Tensor:
+        if self.exchange is not None and self.world > 1:
+            # the exchange and the combine happen inside the merge kernel of this one call
+            ops.decode_paged(q, self.cache, rope, out=self.out, exchange=self.exchange)
+            return self.out
         self.decode_fn(q, self.cache, rope, self.part)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered.view(-1), self.part.view(-1), group=self.group)
