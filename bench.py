@@ -593,6 +593,7 @@ def splitkv_block(args, pkg, dev, rank, world):
                 "bytes_sent_per_rank_per_step": (world - 1) * Hq * (dh + 2) * 4,
                 "merged_vs_single_pass_max_abs": float(st[0].item()), "kernel_status": int(st[1].item()),
                 "achieved_hbm_gbs_all_gpus": alg / (tn_us * 1e-6) / 1e9})
+    ex.close()
     return blk
 
 

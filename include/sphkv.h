@@ -230,6 +230,20 @@ int sphkv_decode_paged(const sphkv_decode_params* p, void* stream);
  * host threads -- race on it and must be serialised by the caller. */
 int sphkv_decode_paged_static(const sphkv_decode_params* p, void* stream);
 
+/* Buffers of the split-KV peer exchange (xchg_recv / xchg_flags of sphkv_decode_params); no
+ * counterpart in the reference, which has no multi-GPU path.  They are written by kernels of
+ * other GPUs, each driven by its own process, so they travel as CUDA IPC handles:
+ *   sphkv_xchg_alloc  cudaMalloc + zero fill on the current device; returns the pointer and the
+ *                     64-byte IPC handle to hand to the other ranks (this call ALLOCATES);
+ *   sphkv_xchg_open   maps another rank's buffer into the current device's address space
+ *                     (peer access is enabled as a side effect); call with the device current
+ *                     whose kernels will store into it, once per handle and process;
+ *   sphkv_xchg_close / sphkv_xchg_free   undo the two. */
+int sphkv_xchg_alloc(int64_t bytes, void** dev_ptr, unsigned char* handle64);
+int sphkv_xchg_open(const unsigned char* handle64, void** dev_ptr);
+int sphkv_xchg_close(void* opened_ptr);
+int sphkv_xchg_free(void* dev_ptr);
+
 /* Log-sum-exp combine of R partial sets, each f32 [n_rows][dh+2] = (max, sum, acc),
  * natural-log max.  Same math as sphkv_reduce_kernel (decode_kernel.cu:221-246) with a
  * plain division (no +1e-8); rows whose total sum is 0 produce zeros.  Used after the

@@ -80,6 +80,10 @@ SIGNATURES = {
     "sphkv_decode_paged_static": (C.c_int, [C.POINTER(DecodeParams), C.c_void_p]),
     "sphkv_merge_partials": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p,
                                        C.c_int32, C.c_void_p]),
+    "sphkv_xchg_alloc": (C.c_int, [C.c_int64, C.POINTER(C.c_void_p), C.c_char_p]),
+    "sphkv_xchg_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "sphkv_xchg_close": (C.c_int, [C.c_void_p]),
+    "sphkv_xchg_free": (C.c_int, [C.c_void_p]),
     "sphkv_pool_decode": (C.c_int, [C.c_void_p] * 13 + [C.c_int32] * 10 + [C.c_float, C.c_int32,
                                                                             C.c_void_p]),
     "sphkv_pool_encode_append": (C.c_int, [C.c_void_p] * 8 + [C.c_int32] * 9 + [C.c_void_p]),

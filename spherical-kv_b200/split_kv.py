@@ -76,47 +76,67 @@ class ExchangeState:
 class PeerExchange(ExchangeState):
     """Receive buffers, flags and step counters of one rank plus the peers' device pointers.
 
-    Every rank allocates its buffers, exports them through CUDA IPC (the handles travel once
-    through `group`), opens the others' and uploads the pointer arrays the kernel reads.  Peer
-    access needs GPUs of one node that can reach each other (NVLink / NVSwitch or PCIe P2P)."""
+    Every rank allocates its two buffers through the library (plain cudaMalloc: one allocation,
+    one IPC handle), the 64-byte handles travel once through `group`, and every rank opens the
+    others' buffers with its own device current -- that is what maps them into this GPU's
+    address space and enables peer access -- then uploads the pointer arrays the kernel reads.
+    Needs GPUs of one node that reach each other (NVLink / NVSwitch or PCIe P2P).  `close()`
+    releases the mappings and the buffers; call it on every rank before the process group goes."""
 
     def __init__(self, B: int, Hq: int, Hkv: int, dh: int, group=None, device=None,
                  timeout_cycles: int = 0):
+        import ctypes as C
+        from . import _lib
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         super().__init__(rank, world, B, Hq, Hkv, dh)
         dev = torch.device(device if device is not None else torch.cuda.current_device())
-        self.timeout_cycles = int(timeout_cycles)
-        self.recv = torch.zeros(self.recv_numel, dtype=torch.float32, device=dev)
-        self.flags = torch.zeros(self.flags_numel, dtype=torch.int32, device=dev)
+        self.device, self.group, self.timeout_cycles = dev, group, int(timeout_cycles)
+        self._lib = _lib
+        lib = _lib.load()
+        self._own, self._opened = [], []
+        with torch.cuda.device(dev):
+            handles = []
+            for nbytes in (self.recv_numel * 4, self.flags_numel * 4):
+                ptr, h = C.c_void_p(), C.create_string_buffer(64)
+                _lib.check(lib.sphkv_xchg_alloc(nbytes, C.byref(ptr), h), "sphkv_xchg_alloc")
+                self._own.append(ptr.value)
+                handles.append(h.raw)
+            recv_ptrs, flag_ptrs = [0] * world, [0] * world
+            recv_ptrs[rank], flag_ptrs[rank] = self._own
+            if world > 1:
+                everyone = [None] * world
+                dist.all_gather_object(everyone, handles, group=group)
+                for q, (h_recv, h_flags) in enumerate(everyone):
+                    if q == rank:
+                        continue
+                    for h, dst in ((h_recv, recv_ptrs), (h_flags, flag_ptrs)):
+                        ptr = C.c_void_p()
+                        _lib.check(lib.sphkv_xchg_open(h, C.byref(ptr)), "sphkv_xchg_open")
+                        self._opened.append(ptr.value)
+                        dst[q] = ptr.value
+                dist.barrier(group=group)  # every rank has opened every buffer before anyone decodes
         self.seq = torch.zeros(self.units, dtype=torch.int32, device=dev)
-        self._peers = []  # keeps the opened peer storages alive
-        recv_ptrs, flag_ptrs = [0] * world, [0] * world
-        recv_ptrs[rank], flag_ptrs[rank] = self.recv.data_ptr(), self.flags.data_ptr()
-        if world > 1:
-            torch.cuda.synchronize(dev)
-            mine = (self.recv.untyped_storage()._share_cuda_(), self.flags.untyped_storage()._share_cuda_())
-            handles = [None] * world
-            dist.all_gather_object(handles, mine, group=group)
-            for q, (h_recv, h_flags) in enumerate(handles):
-                if q == rank:
-                    continue
-                t_recv = self._open(h_recv, torch.float32, self.recv_numel)
-                t_flags = self._open(h_flags, torch.int32, self.flags_numel)
-                self._peers.append((t_recv, t_flags))
-                recv_ptrs[q], flag_ptrs[q] = t_recv.data_ptr(), t_flags.data_ptr()
-            dist.barrier(group=group)  # every rank has opened every buffer before anyone decodes
         self.recv_ptrs = torch.tensor(recv_ptrs, dtype=torch.int64, device=dev)
         self.flag_ptrs = torch.tensor(flag_ptrs, dtype=torch.int64, device=dev)
-
-    @staticmethod
-    def _open(handle, dtype, numel):
-        storage = torch.UntypedStorage._new_shared_cuda(*handle)
-        return torch.empty(0, dtype=dtype, device=storage.device).set_(storage, 0, (numel,))
 
     def check_shape(self, B: int, Hq: int, Hkv: int, dh: int) -> None:
         if (B, Hq, Hkv, dh) != (self.B, self.Hq, self.Hkv, self.dh):
             raise ValueError("PeerExchange was sized for another (B, Hq, Hkv, dh)")
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers, waits for every rank to have done so, frees this rank's."""
+        lib = self._lib.load()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for ptr in self._opened:
+                lib.sphkv_xchg_close(ptr)
+            self._opened = []
+            if self.world > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)
+            for ptr in self._own:
+                lib.sphkv_xchg_free(ptr)
+            self._own = []
 
 
 class SplitKVDecoder:
