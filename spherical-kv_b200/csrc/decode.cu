@@ -645,17 +645,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
         const int g = tg.g[s], bits = tg.bits[s], G = DH / g, cpr = g >> 2;
         const int dup = a.cb_dup[s];
         const float* src = p.codebooks + ((int64_t)(hkv * tg.n_slots + s) * tg.G_max) * tg.C_max * tg.g_max;
-        float4* dst = reinterpret_cast<float4*>(cb_smem + a.cb_smem_off[s]);
+        const uint32_t dst = cb_u32 + a.cb_smem_off[s];
         const int chunks = (G << bits) * cpr;
+        // asynchronous 16-byte copies: every chunk of the codebook is in flight at once instead
+        // of one load-store round trip per loop iteration (the caller waits for the group)
         for (int i = threadIdx.x; i < chunks; i += blockDim.x) {
           const int c4 = i % cpr, row = i / cpr;
           const int c = row & ((1 << bits) - 1), gam = row >> bits;
-          const float4 v = __ldg(reinterpret_cast<const float4*>(src + ((int64_t)gam * tg.C_max + c) * tg.g_max) + c4);
+          const float4* sp = reinterpret_cast<const float4*>(src + ((int64_t)gam * tg.C_max + c) * tg.g_max) + c4;
           if (dup) {
-            dst[row * 8 + c4] = v;
-            dst[row * 8 + 4 + c4] = v;
+            cp_async_16(dst + (row * 8 + c4) * 16, sp);
+            cp_async_16(dst + (row * 8 + 4 + c4) * 16, sp);
           } else {
-            dst[i] = v;
+            cp_async_16(dst + i * 16, sp);
           }
         }
       }
@@ -716,9 +718,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
     __syncthreads();     // the previous segment is done with shared memory
     meta_stage0(0);
     stage_codebooks();
+    cp_async_commit();
     meta_stage1();
     load_q();
     meta_stage2(0);
+    cp_async_wait<0>();  // the codebook copies of this thread; the barrier publishes everyone's
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < kVStages - 1; ++i) issue_v(i);
