@@ -11,12 +11,18 @@
 #ifndef SPHKV_SEARCH_UNROLL
 #define SPHKV_SEARCH_UNROLL 2
 #endif
+// all-tier code kernel: tokens per thread (4 = one CTA of 8 warps per SM, 232 registers; 2 = two
+// CTAs per SM) and the unroll factor of its centroid loop
 #ifndef SPHKV_CODE_TOKENS
-#define SPHKV_CODE_TOKENS 2
+#define SPHKV_CODE_TOKENS 4
+#endif
+#ifndef SPHKV_CODE_UNROLL
+#define SPHKV_CODE_UNROLL 4
 #endif
 #define SPHKV_PRAGMA_(x) _Pragma(#x)
 #define SPHKV_PRAGMA(x) SPHKV_PRAGMA_(x)
 #define SPHKV_UNROLL_SEARCH SPHKV_PRAGMA(unroll SPHKV_SEARCH_UNROLL)
+#define SPHKV_UNROLL_CODE_SEARCH SPHKV_PRAGMA(unroll SPHKV_CODE_UNROLL)
 
 namespace sphkv {
 
@@ -79,6 +85,15 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t sme
 }
 __device__ __forceinline__ void cp_async_16(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gptr));
+}
+// 16-byte asynchronous copy of which only the first src_bytes (0 or 16) are read; the rest is zero
+__device__ __forceinline__ void cp_async_16_zfill(uint32_t smem_addr, const void* gptr, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gptr), "r"(src_bytes));
+}
+__device__ __forceinline__ float4 lds_f4(uint32_t smem_addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_addr));
+  return v;
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>

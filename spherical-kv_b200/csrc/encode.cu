@@ -16,6 +16,7 @@
 //   scale = max_t r ; code = clamp(rint((r / max(scale, 1e-8)) * 127), -127, 127)
 // The similarity is taken on the un-normalised group vector: dividing by r first
 // (spherical_kv_pipeline.py:1138) scales every sim_c by the same positive factor.
+#include <algorithm>
 #include "common.cuh"
 
 namespace sphkv {
@@ -23,9 +24,22 @@ namespace sphkv {
 struct EncodeArgs {
   sphkv_encode_params p;
   int bundles_per_cta;
+  int warp_smem_bytes;  // page assembly: shared memory of one warp
 };
 
 constexpr int kEncThreads = 256;
+
+// two 16-bit elements (bf16 or f16) of one 32-bit word, widened exactly
+__device__ __forceinline__ void unpack16(uint32_t w, int dtype, float& lo, float& hi) {
+  if (dtype == SPHKV_BF16) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+  } else {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w);
+    lo = __low2float(h);
+    hi = __high2float(h);
+  }
+}
 
 template <int GS>
 __device__ __forceinline__ void load_group(const void* base, int dtype, int64_t off, float (&k)[GS]) {
@@ -44,16 +58,7 @@ __device__ __forceinline__ void load_group(const void* base, int dtype, int64_t 
       const uint4 v = __ldg(s + i);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (dtype == SPHKV_BF16) {
-          k[8 * i + 2 * e] = __uint_as_float(w[e] << 16);
-          k[8 * i + 2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-        } else {
-          const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
-          k[8 * i + 2 * e] = __low2float(h);
-          k[8 * i + 2 * e + 1] = __high2float(h);
-        }
-      }
+      for (int e = 0; e < 4; ++e) unpack16(w[e], dtype, k[8 * i + 2 * e], k[8 * i + 2 * e + 1]);
     }
   } else {
 #pragma unroll
@@ -61,14 +66,41 @@ __device__ __forceinline__ void load_group(const void* base, int dtype, int64_t 
   }
 }
 
+// Eight consecutive V elements starting at element offset `off` of v_src, as one 16-byte chunk
+// of the 16-bit V pool (copied when the types agree, else rounded to nearest even).
+__device__ __forceinline__ uint4 load_v_chunk(const sphkv_encode_params& p, bool same, int64_t off) {
+  if (same && (((uintptr_t)p.v_src + off * 2) & 15) == 0)
+    return __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.v_src) + off));
+  float v[8];
+  if (p.v_src_dtype == SPHKV_F32 && (((uintptr_t)p.v_src + off * 4) & 15) == 0) {
+    const float4 a0 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off));
+    const float4 a1 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off + 4));
+    v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
+    v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = load_as_float(p.v_src, p.v_src_dtype, off + e);
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    if (p.v_pool_dtype == SPHKV_F16) {
+      w[e] = pack_f16x2(v[2 * e], v[2 * e + 1]);
+    } else {
+      __nv_bfloat162 hb2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+      w[e] = *reinterpret_cast<uint32_t*>(&hb2);
+    }
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 constexpr int kMaxBundlesPerCta = 8;  // consecutive bundles one CTA walks (they mostly share a codebook)
 
 // PHASE 0: everything in one kernel (no scratch needed).  PHASE 1: radius + nearest-centroid
 // search only, results to the scratch arrays r[(page*N + slot) * (dh/16) + group] (f32) and
-// theta[...] (u8).  PHASE 2: page assembly + V pages from those arrays.  Splitting lets the
-// FMA-bound search run without the barriers and small dependent loads of the page bookkeeping.
-// PHASE 3: page assembly from a per-token code cache (sphkv_encode_codes) gathered through
-// src_index: re-paging after a tier change without touching the dense keys.
+// theta[...] (u8); assemble_pages_kernel then builds the pages and the V pages from those arrays.
+// Splitting lets the FMA-bound search run without the barriers and small dependent loads of the
+// page bookkeeping.
 template <int GS, int PHASE>
 __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const EncodeArgs a) {
   const sphkv_encode_params& p = a.p;
@@ -80,7 +112,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   const int G = dh / GS, g_shift = 31 - __clz(G);
   const int n_shift = 31 - __clz(N);  // page_size is a power of two
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-  const int C_cap = PHASE >= 2 ? 0 : p.tiers.C_max;
+  const int C_cap = p.tiers.C_max;
   const int GST = dh >> 4;  // group stride of the scratch arrays
   float* scr_r = reinterpret_cast<float*>(p.scratch);
   uint8_t* scr_t = reinterpret_cast<uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
@@ -129,7 +161,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     const int img_stride = ((8 + 4 * G + (N * G * bits + 7) / 8 + N * G * rb) + 15) & ~15;
 
     // ---- codebook of (head, slot) -> shared memory, 128-bit copies ---------------------------
-    if (PHASE < 2 && head * p.tiers.n_slots + slot != loaded_key) {
+    if (head * p.tiers.n_slots + slot != loaded_key) {
       const float4* src = reinterpret_cast<const float4*>(
           p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
                             p.tiers.g_max);
@@ -147,7 +179,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
     }
 
     // ---- radius + nearest centroid: warp = group, lane = token slots lane + 32 h, h < 4 ----
-    if (PHASE < 2 && warp < G) {
+    if (warp < G) {
       const float* cbg = cb_s + (warp << bits) * GS;
       float k[4][GS];
       bool have[4];
@@ -175,8 +207,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
       float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       int code[4] = {0, 0, 0, 0};
       SPHKV_UNROLL_SEARCH
-      SPHKV_UNROLL_SEARCH
-  for (int c = 0; c < C; ++c) {
+      for (int c = 0; c < C; ++c) {
         const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
         float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -213,43 +244,6 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
       }
     }
     if (PHASE == 1) continue;  // the assembly launch takes it from here
-    if (PHASE == 2) {
-      for (int i = threadIdx.x; i < TB * G; i += blockDim.x) {
-        const int ts = i >> g_shift, gq = i & (G - 1);
-        const int q = ts >> n_shift, tin = ts & (N - 1);
-        const int page = page_s[q];
-        float rv = 0.f;
-        uint8_t tv = 0;
-        if (page >= 0) {
-          const int64_t si = ((int64_t)page * N + tin) * GST + gq;
-          rv = scr_r[si];
-          tv = scr_t[si];
-        }
-        r_s[i] = rv;
-        th_s[i] = tv;
-      }
-    }
-    if (PHASE == 3) {
-      const float* cr = p.code_r[slot];
-      const uint8_t* ct = p.code_theta[slot];
-      for (int i = threadIdx.x; i < TB * G; i += blockDim.x) {
-        const int ts = i >> g_shift, gq = i & (G - 1);
-        const int q = ts >> n_shift, tin = ts & (N - 1);
-        const int page = page_s[q];
-        float rv = 0.f;
-        uint8_t tv = 0;
-        if (page >= 0) {
-          const int64_t row = p.src_index[(int64_t)page * N + tin];
-          if (row >= 0) {
-            const int64_t ci = ((int64_t)head * p.code_rows + row) * G + gq;
-            rv = cr[ci];
-            tv = ct[ci];
-          }
-        }
-        r_s[i] = rv;
-        th_s[i] = tv;
-      }
-    }
     __syncthreads();
 
     // ---- per-page, per-group scale = max radius over the page's tokens ----------------------
@@ -389,37 +383,150 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
         uint4 o[kInFlight];
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u) {
-          o[u] = make_uint4(0u, 0u, 0u, 0u);
-          if (!live[u]) continue;
-          if (same && (((uintptr_t)p.v_src + off[u] * 2) & 15) == 0) {
-            o[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.v_src) + off[u]));
-          } else {
-            float v[8];
-            if (p.v_src_dtype == SPHKV_F32 && (((uintptr_t)p.v_src + off[u] * 4) & 15) == 0) {
-              const float4 a0 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off[u]));
-              const float4 a1 = ldg_stream_f4(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.v_src) + off[u] + 4));
-              v[0] = a0.x; v[1] = a0.y; v[2] = a0.z; v[3] = a0.w;
-              v[4] = a1.x; v[5] = a1.y; v[6] = a1.z; v[7] = a1.w;
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = load_as_float(p.v_src, p.v_src_dtype, off[u] + e);
-            }
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              if (p.v_pool_dtype == SPHKV_F16) {
-                w[e] = pack_f16x2(v[2 * e], v[2 * e + 1]);
-              } else {
-                __nv_bfloat162 hb2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                w[e] = *reinterpret_cast<uint32_t*>(&hb2);
-              }
-            }
-            o[u] = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          o[u] = live[u] ? load_v_chunk(p, same, off[u]) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u)
           if (dst[u] >= 0) reinterpret_cast<uint4*>(p.v_pool)[dst[u]] = o[u];
+      }
+    }
+  }
+}
+
+// ---- page assembly, one warp per page -----------------------------------------------------
+// Builds page images from per-(token, group) radii and centroid indices that already exist:
+// SRC 2 = the scratch arrays the search launch wrote ([(page * N + slot) * (dh / 16) + group]),
+// SRC 3 = a per-token code cache (sphkv_encode_codes) gathered through src_index, i.e. re-paging
+// after a tier change without touching the dense keys.  A warp owns a page from the first
+// lookup to the last byte, so there is no CTA barrier and the only dependent global loads are
+// page index -> src_index row -> code; with 64 warps per SM thousands of pages are in flight.
+// Per-warp shared memory: rows i32[N] | r f32[N*G] | scale f32[8] | theta u8[N*G] | page image.
+template <int SRC>
+__global__ void __launch_bounds__(kEncThreads) assemble_pages_kernel(const EncodeArgs a) {
+  const sphkv_encode_params& p = a.p;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int N = p.page_size, dh = p.dh, GST = dh >> 4;
+  const int ppb = 128 / N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* mine = smem + (size_t)warp * a.warp_smem_bytes;
+  int* rows_w = reinterpret_cast<int*>(mine);
+  float* r_w = reinterpret_cast<float*>(rows_w + N);
+  float* scale_w = r_w + N * GST;
+  uint8_t* th_w = reinterpret_cast<uint8_t*>(scale_w + 8);
+  uint8_t* img = th_w + N * GST;  // 16-byte aligned: every term above is a multiple of 16
+  const float* scr_r = reinterpret_cast<const float*>(p.scratch);
+  const uint8_t* scr_t = reinterpret_cast<const uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
+  const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
+  const int64_t items = (int64_t)p.n_bundles * ppb;
+  for (int64_t it = (int64_t)blockIdx.x * (kEncThreads / 32) + warp; it < items; it += (int64_t)gridDim.x * (kEncThreads / 32)) {
+    const int page = p.bundles[8 * (it / ppb) + it % ppb];
+    if (page < 0) continue;
+    const int head = p.page_head[page], slot = p.page_slot[page];
+    const int64_t poff = p.ptable[3 * (int64_t)page];
+    const int gs = p.tiers.g[slot], bits = p.tiers.bits[slot];
+    const int G = dh / gs, g_shift = 31 - __clz(G);
+    __syncwarp();  // the previous page's image has been copied out
+    // ---- source rows and the valid-token count (valid slots form a prefix) -------------------
+    int cnt = 0;
+    for (int t0 = 0; t0 < N; t0 += 32) {
+      const int row = t0 + lane < N ? p.src_index[(int64_t)page * N + t0 + lane] : -1;
+      if (t0 + lane < N) rows_w[t0 + lane] = row;
+      cnt += __popc(__ballot_sync(0xffffffffu, row >= 0));
+    }
+    __syncwarp();
+    // ---- radii and centroid indices of the page -----------------------------------------------
+    for (int i = lane; i < N * G; i += 32) {
+      const int tin = i >> g_shift, gq = i & (G - 1);
+      float rv = 0.f;
+      uint8_t tv = 0;
+      if (SRC == 2) {
+        const int64_t si = ((int64_t)page * N + tin) * GST + gq;
+        rv = scr_r[si];
+        tv = scr_t[si];
+      } else {
+        const int row = rows_w[tin];
+        if (row >= 0) {
+          const int64_t ci = ((int64_t)head * p.code_rows + row) * G + gq;
+          rv = p.code_r[slot][ci];
+          tv = p.code_theta[slot][ci];
+        }
+      }
+      r_w[i] = rv;
+      th_w[i] = tv;
+    }
+    __syncwarp();
+    // ---- per-group scale = max radius over the page's tokens ----------------------------------
+    {
+      const int gq = lane & 7, tq = lane >> 3;
+      float mx = 0.f;
+      if (gq < G)
+        for (int t = tq; t < cnt; t += 4) mx = fmaxf(mx, r_w[t * G + gq]);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+      if (lane < 8) scale_w[lane] = mx;
+    }
+    __syncwarp();
+    if (cnt > 0) {
+      // ---- header, scales, LSB-first theta words ----------------------------------------------
+      const int hdr = 8 + 4 * G;
+      const int nvals = cnt * G;
+      const int th_bytes = (nvals * bits + 7) >> 3;
+      const int th_words = (th_bytes + 3) >> 2;
+      if (lane < 2)
+        reinterpret_cast<uint32_t*>(img)[lane] =
+            lane == 0 ? (uint32_t)(p.tiers.tier_id[slot] & 0xFF) | ((uint32_t)(cnt & 0xFF) << 8) |
+                            ((uint32_t)(p.radius_fmt & 0xFF) << 16)
+                      : 0u;
+      if (lane < G) reinterpret_cast<float*>(img + 8)[lane] = scale_w[lane];
+      for (int w = lane; w < th_words; w += 32) {
+        const int bit0 = w * 32;
+        int i = bit0 / bits;  // first value overlapping this word
+        uint32_t acc = 0;
+        for (; i < nvals && i * bits < bit0 + 32; ++i) {
+          const uint32_t v = th_w[i];
+          const int sh = i * bits - bit0;
+          acc |= sh >= 0 ? (v << sh) : (v >> (-sh));
+        }
+        reinterpret_cast<uint32_t*>(img + hdr)[w] = acc;
+      }
+      __syncwarp();
+      // ---- radii (may overlay the zero tail of the last theta word) ---------------------------
+      uint8_t* rad = img + hdr + th_bytes;
+      for (int i = lane; i < nvals; i += 32) {
+        const float rr = r_w[i];
+        if (rb == 1) {
+          const float safe = fmaxf(scale_w[i & (G - 1)], 1e-8f);
+          float qv = rintf(__fmul_rn(__fdiv_rn(rr, safe), 127.0f));
+          qv = fminf(fmaxf(qv, -127.f), 127.f);
+          rad[i] = (uint8_t)(int8_t)(int)qv;
+        } else {
+          // the half's bit pattern goes over the radius slot as a 32-bit word (this lane read it
+          // just above); its two bytes are laid into the image below
+          reinterpret_cast<uint32_t*>(r_w)[i] = (uint32_t)__half_as_ushort(__float2half_rn(rr));
+        }
+      }
+      __syncwarp();
+      if (rb == 2) {
+        const uint8_t* hb = reinterpret_cast<const uint8_t*>(r_w);
+        for (int b2 = lane; b2 < 2 * nvals; b2 += 32) rad[b2] = hb[(b2 >> 1) * 4 + (b2 & 1)];
+        __syncwarp();
+      }
+      // ---- copy the image out ----------------------------------------------------------------
+      const int bytes = hdr + th_bytes + nvals * rb;
+      for (int w = lane; w < (bytes >> 2); w += 32)
+        reinterpret_cast<uint32_t*>(p.k_pages + poff)[w] = reinterpret_cast<const uint32_t*>(img)[w];
+      if (lane < (bytes & 3)) p.k_pages[poff + (bytes & ~3) + lane] = img[(bytes & ~3) + lane];
+    }
+    // ---- dense V page (16-bit), empty slots zero-filled ---------------------------------------
+    if (p.v_src != nullptr && p.v_pool != nullptr) {
+      const int pr_shift = 31 - __clz(dh >> 3);  // 16-byte chunks per row (dh / 8, a power of two)
+      const bool same = p.v_src_dtype == p.v_pool_dtype;
+      for (int i = lane; i < (N << pr_shift); i += 32) {
+        const int tin = i >> pr_shift, d = (i & ((1 << pr_shift) - 1)) * 8;
+        const int row = rows_w[tin];
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (row >= 0) o = load_v_chunk(p, same, (int64_t)row * p.v_row_stride + (int64_t)head * p.v_head_stride + d);
+        reinterpret_cast<uint4*>(p.v_pool)[(((int64_t)page * N + tin) * dh + d) >> 3] = o;
       }
     }
   }
@@ -439,12 +546,14 @@ struct CodesArgs {
   float* r_out[SPHKV_MAX_TIER_SLOTS];
   uint8_t* th_out[SPHKV_MAX_TIER_SLOTS];
   int64_t k_row_stride, k_head_stride, rows;
+  int64_t n_units, units_per_head;  // unit = one CTA pass: (8 / (dh / 32)) * 32 * kCodeTok rows of one head
   int k_dtype, dh;
+  int kbuf_off;  // byte offset of the staged row blocks (8 warps x 32 * kCodeTok rows x 128 B)
   int cb_off[SPHKV_MAX_TIER_SLOTS];  // float offset of each slot's staged codebook
   sphkv_tiers tiers;
 };
 
-// tokens per thread of the code-cache kernel: 2 keeps it at two CTAs per SM (<= 128 registers)
+// tokens per thread of the code-cache kernel
 constexpr int kCodeTok = SPHKV_CODE_TOKENS;
 
 template <int OFF, int GS>
@@ -453,7 +562,7 @@ __device__ __forceinline__ void search_slice(const float (&k)[kCodeTok][32], con
   float best[kCodeTok];
 #pragma unroll
   for (int h = 0; h < kCodeTok; ++h) { best[h] = -INFINITY; code[h] = 0; }
-  SPHKV_UNROLL_SEARCH
+  SPHKV_UNROLL_CODE_SEARCH
   for (int c = 0; c < C; ++c) {
     const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
     float sacc[kCodeTok];
@@ -476,88 +585,174 @@ __device__ __forceinline__ void search_slice(const float (&k)[kCodeTok][32], con
   }
 }
 
-__global__ void __launch_bounds__(kEncThreads, kCodeTok <= 2 ? 2 : 1) encode_codes_kernel(const CodesArgs a) {
+// CTAs per SM of the code-cache kernel (2 tokens per thread fit 128 registers, 4 need 232)
+constexpr int kCodeCtasPerSm = kCodeTok <= 2 ? 2 : 1;
+#ifndef SPHKV_CODE_WARPS
+#define SPHKV_CODE_WARPS 8
+#endif
+constexpr int kCodeThreads = SPHKV_CODE_WARPS * 32;  // a multiple of four warps: dh / 32 warps share a token set
+
+// Persistent: the (head, row block) units are dealt out in contiguous runs, one run per resident
+// CTA.  A CTA stages a head's codebooks when its run enters that head (once or twice per CTA) and
+// has no other barrier, so the warps of an SM drift apart and one warp's key loads hide under the
+// others' searches.  STAGED: a warp's next row block travels global -> shared memory by 16-byte
+// asynchronous copies (eight lanes per 128-byte row slice, so every sector is used whole) while
+// the current block is searched; the chunk index is XOR-ed with the row so that both the copies
+// and the later one-row-per-lane 128-bit reads touch every bank once.  Not STAGED (slices not
+// 16-byte aligned, or no room beside the codebooks): each lane loads its own rows and asks L2
+// for the next block's rows a block ahead.
+template <bool STAGED>
+__global__ void __launch_bounds__(kCodeThreads, kCodeCtasPerSm) encode_codes_kernel(const CodesArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   float* cb_s = reinterpret_cast<float*>(smem);
-  const int head = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G32 = a.dh >> 5;                  // 32-dim groups per head: 2 or 4
   const int grp = warp % G32, set = warp / G32;
-  const int sets = (kEncThreads / 32) / G32;  // token sets of 32 * kCodeTok per CTA
-  // stage every slot's codebook of this head: [G_s][C_s][g_s] packed
-  for (int s = 0; s < a.tiers.n_slots; ++s) {
-    const int gs = a.tiers.g[s], bits = a.tiers.bits[s], G = a.dh / gs, q4n = gs >> 2;
-    const float4* src = reinterpret_cast<const float4*>(
-        a.codebooks + ((int64_t)(head * a.tiers.n_slots + s) * a.tiers.G_max) * a.tiers.C_max * a.tiers.g_max);
-    float4* dst = reinterpret_cast<float4*>(cb_s + a.cb_off[s]);
-    const int total = (G << bits) * q4n, row_stride4 = a.tiers.g_max >> 2;
-    for (int i = threadIdx.x; i < total; i += blockDim.x) {
-      const int q4 = i % q4n, row = i / q4n;
-      dst[i] = __ldg(src + ((int64_t)(row >> bits) * a.tiers.C_max + (row & ((1 << bits) - 1))) * row_stride4 + q4);
-    }
-  }
-  __syncthreads();
-
-  const int64_t row0 = ((int64_t)blockIdx.x * sets + set) * (32 * kCodeTok);
-  float k[kCodeTok][32];
-  bool have[kCodeTok];
+  const int sets = (kCodeThreads / 32) / G32;  // token sets of 32 * kCodeTok per CTA
+  constexpr int kBlockRows = 32 * kCodeTok;
+  const int esize = a.k_dtype == SPHKV_F32 ? 4 : 2;
+  const int64_t u_lo = a.n_units * blockIdx.x / gridDim.x, u_hi = a.n_units * (blockIdx.x + 1) / gridDim.x;
+  const bool k32 = a.k_dtype == SPHKV_F32;
+  const uint32_t kbuf = smem_u32(smem + a.kbuf_off) + warp * (kBlockRows * 128);  // this warp's row block
+  auto issue_block = [&](int64_t uu) {
+    const int64_t hd = uu / a.units_per_head;
+    const int64_t c0 = hd * a.k_head_stride + grp * 32;
+    const int64_t r0 = ((uu - hd * a.units_per_head) * sets + set) * kBlockRows;
+    const char* base = reinterpret_cast<const char*>(a.k_src);
+    if (k32) {
 #pragma unroll
-  for (int h = 0; h < kCodeTok; ++h) {
-    const int64_t row = row0 + lane + 32 * h;
-    have[h] = row < a.rows;
-    if (have[h]) {
-      load_group<32>(a.k_src, a.k_dtype, row * a.k_row_stride + (int64_t)head * a.k_head_stride + grp * 32, k[h]);
+      for (int i = 0; i < kCodeTok * 8; ++i) {
+        const int f = i * 32 + lane, r = f >> 3, c = f & 7;
+        const bool in = r0 + r < a.rows;
+        cp_async_16_zfill(kbuf + r * 128 + ((c ^ (r & 7)) << 4),
+                          in ? base + ((r0 + r) * a.k_row_stride + c0) * 4 + c * 16 : base, in ? 16 : 0);
+      }
     } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) k[h][i] = 0.f;
+      for (int i = 0; i < kCodeTok * 4; ++i) {
+        const int f = i * 32 + lane, r = f >> 2, c = f & 3;
+        const bool in = r0 + r < a.rows;
+        cp_async_16_zfill(kbuf + r * 64 + ((c ^ ((r >> 1) & 3)) << 4),
+                          in ? base + ((r0 + r) * a.k_row_stride + c0) * 2 + c * 16 : base, in ? 16 : 0);
+      }
     }
-  }
-  float na[kCodeTok], nb[kCodeTok], nab[kCodeTok];
+    cp_async_commit();
+  };
+  if (STAGED && u_lo < u_hi) issue_block(u_lo);
+  int head = -1;
+  for (int64_t u = u_lo; u < u_hi; ++u) {
+    const int u_head = (int)(u / a.units_per_head);
+    if (u_head != head) {
+      // stage every slot's codebook of this head: [G_s][C_s][g_s] packed
+      if (head >= 0) __syncthreads();
+      head = u_head;
+      for (int s = 0; s < a.tiers.n_slots; ++s) {
+        const int gs = a.tiers.g[s], bits = a.tiers.bits[s], G = a.dh / gs, q4n = gs >> 2;
+        const float4* src = reinterpret_cast<const float4*>(
+            a.codebooks + ((int64_t)(head * a.tiers.n_slots + s) * a.tiers.G_max) * a.tiers.C_max * a.tiers.g_max);
+        float4* dst = reinterpret_cast<float4*>(cb_s + a.cb_off[s]);
+        const int total = (G << bits) * q4n, row_stride4 = a.tiers.g_max >> 2;
+        for (int i = threadIdx.x; i < total; i += blockDim.x) {
+          const int q4 = i % q4n, row = i / q4n;
+          dst[i] = __ldg(src + ((int64_t)(row >> bits) * a.tiers.C_max + (row & ((1 << bits) - 1))) * row_stride4 + q4);
+        }
+      }
+      __syncthreads();
+    }
+    const int64_t col = (int64_t)head * a.k_head_stride + grp * 32;
+    const int64_t row0 = ((u - (int64_t)head * a.units_per_head) * sets + set) * kBlockRows;
+    if (!STAGED && u + 1 < u_hi) {
+      const int64_t ncol = (u + 1) / a.units_per_head * a.k_head_stride + grp * 32;
+      const int64_t nrow0 = ((u + 1) % a.units_per_head * sets + set) * kBlockRows;
 #pragma unroll
-  for (int h = 0; h < kCodeTok; ++h) na[h] = nb[h] = 0.f;
+      for (int h = 0; h < kCodeTok; ++h) {
+        const int64_t nrow = nrow0 + lane + 32 * h;
+        if (nrow < a.rows)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(a.k_src) + (nrow * a.k_row_stride + ncol) * esize));
+      }
+    }
+    float k[kCodeTok][32];
+    bool have[kCodeTok];
+    if (STAGED) {
+      cp_async_wait<0>();
+      __syncwarp();
 #pragma unroll
-  for (int d = 0; d < 16; ++d)
+      for (int h = 0; h < kCodeTok; ++h) {
+        have[h] = row0 + lane + 32 * h < a.rows;
+        const int r = h * 32 + lane;
+        if (k32) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 v = lds_f4(kbuf + r * 128 + ((c ^ (lane & 7)) << 4));
+            k[h][4 * c] = v.x; k[h][4 * c + 1] = v.y; k[h][4 * c + 2] = v.z; k[h][4 * c + 3] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const float4 v = lds_f4(kbuf + r * 64 + ((c ^ ((lane >> 1) & 3)) << 4));
+            const uint32_t w[4] = {__float_as_uint(v.x), __float_as_uint(v.y), __float_as_uint(v.z), __float_as_uint(v.w)};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) unpack16(w[e], a.k_dtype, k[h][8 * c + 2 * e], k[h][8 * c + 2 * e + 1]);
+          }
+        }
+      }
+      __syncwarp();
+      if (u + 1 < u_hi) issue_block(u + 1);
+    } else
 #pragma unroll
     for (int h = 0; h < kCodeTok; ++h) {
-      na[h] = __fmaf_rn(k[h][d], k[h][d], na[h]);
-      nb[h] = __fmaf_rn(k[h][16 + d], k[h][16 + d], nb[h]);
+      const int64_t row = row0 + lane + 32 * h;
+      have[h] = row < a.rows;
+      if (have[h]) {
+        load_group<32>(a.k_src, a.k_dtype, row * a.k_row_stride + col, k[h]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) k[h][i] = 0.f;
+      }
     }
+    float na[kCodeTok], nb[kCodeTok], nab[kCodeTok];
 #pragma unroll
-  for (int h = 0; h < kCodeTok; ++h) nab[h] = na[h];
+    for (int h = 0; h < kCodeTok; ++h) na[h] = nb[h] = 0.f;
 #pragma unroll
-  for (int d = 16; d < 32; ++d)
+    for (int d = 0; d < 16; ++d)
 #pragma unroll
-    for (int h = 0; h < kCodeTok; ++h) nab[h] = __fmaf_rn(k[h][d], k[h][d], nab[h]);
+      for (int h = 0; h < kCodeTok; ++h) {
+        na[h] = __fmaf_rn(k[h][d], k[h][d], na[h]);
+        nb[h] = __fmaf_rn(k[h][16 + d], k[h][16 + d], nb[h]);
+      }
+#pragma unroll
+    for (int h = 0; h < kCodeTok; ++h) nab[h] = na[h];
+#pragma unroll
+    for (int d = 16; d < 32; ++d)
+#pragma unroll
+      for (int h = 0; h < kCodeTok; ++h) nab[h] = __fmaf_rn(k[h][d], k[h][d], nab[h]);
 
-  for (int s = 0; s < a.tiers.n_slots; ++s) {
-    if (a.r_out[s] == nullptr) continue;
-    const int bits = a.tiers.bits[s], C = 1 << bits;
-    int code[kCodeTok];
-    if (a.tiers.g[s] == 16) {
-      const int G = a.dh >> 4;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int gam = 2 * grp + half;
-        if (half == 0)
-          search_slice<0, 16>(k, cb_s + a.cb_off[s] + (gam << bits) * 16, C, code);
-        else
-          search_slice<16, 16>(k, cb_s + a.cb_off[s] + (gam << bits) * 16, C, code);
+    for (int s = 0; s < a.tiers.n_slots; ++s) {
+      if (a.r_out[s] == nullptr) continue;
+      const int bits = a.tiers.bits[s], C = 1 << bits;
+      if (a.tiers.g[s] == 16) {
+        // both 16-dim halves of the slice, stored as one 8-byte radius pair and one 2-byte code pair
+        const int G = a.dh >> 4;
+        int code_a[kCodeTok], code_b[kCodeTok];
+        search_slice<0, 16>(k, cb_s + a.cb_off[s] + ((2 * grp) << bits) * 16, C, code_a);
+        search_slice<16, 16>(k, cb_s + a.cb_off[s] + ((2 * grp + 1) << bits) * 16, C, code_b);
 #pragma unroll
         for (int h = 0; h < kCodeTok; ++h) {
           if (!have[h]) continue;
-          const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G + gam;
-          a.r_out[s][o] = __fsqrt_rn(half == 0 ? na[h] : nb[h]);
+          const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G + 2 * grp;
+          *reinterpret_cast<float2*>(a.r_out[s] + o) = make_float2(__fsqrt_rn(na[h]), __fsqrt_rn(nb[h]));
+          *reinterpret_cast<uint16_t*>(a.th_out[s] + o) = (uint16_t)(code_a[h] | (code_b[h] << 8));
+        }
+      } else {
+        int code[kCodeTok];
+        search_slice<0, 32>(k, cb_s + a.cb_off[s] + (grp << bits) * 32, C, code);
+#pragma unroll
+        for (int h = 0; h < kCodeTok; ++h) {
+          if (!have[h]) continue;
+          const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G32 + grp;
+          a.r_out[s][o] = __fsqrt_rn(nab[h]);
           a.th_out[s][o] = (uint8_t)code[h];
         }
-      }
-    } else {
-      search_slice<0, 32>(k, cb_s + a.cb_off[s] + (grp << bits) * 32, C, code);
-#pragma unroll
-      for (int h = 0; h < kCodeTok; ++h) {
-        if (!have[h]) continue;
-        const int64_t o = ((int64_t)head * a.rows + row0 + lane + 32 * h) * G32 + grp;
-        a.r_out[s][o] = __fsqrt_rn(nab[h]);
-        a.th_out[s][o] = (uint8_t)code[h];
       }
     }
   }
@@ -570,20 +765,34 @@ int validate_tiers(const sphkv_tiers& t, int dh);
 using namespace sphkv;
 
 template <int GS>
-static int launch_encode(const EncodeArgs& a, bool split, bool from_codes, int smem_bytes, cudaStream_t st) {
+static int launch_encode(const EncodeArgs& a, bool split, int smem_bytes, cudaStream_t st) {
   const int grid = (a.p.n_bundles + a.bundles_per_cta - 1) / a.bundles_per_cta;
-  if (from_codes) {
-    encode_bundle_kernel<GS, 3><<<grid, kEncThreads, smem_bytes, st>>>(a);
-    return check_launch("encode_bundle_kernel<from codes>");
-  }
   if (split) {
     encode_bundle_kernel<GS, 1><<<grid, kEncThreads, smem_bytes, st>>>(a);
-    if (int rc = check_launch("encode_bundle_kernel<search>")) return rc;
-    encode_bundle_kernel<GS, 2><<<grid, kEncThreads, smem_bytes, st>>>(a);
-    return check_launch("encode_bundle_kernel<assemble>");
+    return check_launch("encode_bundle_kernel<search>");
   }
   encode_bundle_kernel<GS, 0><<<grid, kEncThreads, smem_bytes, st>>>(a);
   return check_launch("encode_bundle_kernel<fused>");
+}
+
+// One warp per page of the bundle list, every tier slot in the same launch.
+static int launch_assemble(EncodeArgs& a, bool from_codes, cudaStream_t st) {
+  const sphkv_encode_params& p = a.p;
+  const int N = p.page_size, GST = p.dh >> 4;
+  const int img = ((8 + 4 * GST + N * GST + N * GST * 2) + 15) & ~15;  // 8-bit codes, f16 radii: the largest image
+  a.warp_smem_bytes = 4 * N + 4 * N * GST + 32 + N * GST + img;
+  const int smem_bytes = a.warp_smem_bytes * (kEncThreads / 32);
+  static SmemOptIn opt_in[2];
+  const void* fn = from_codes ? (const void*)assemble_pages_kernel<3> : (const void*)assemble_pages_kernel<2>;
+  if (int rc = ensure_dynamic_smem(opt_in[from_codes], fn, smem_bytes, "assemble_pages")) return rc;
+  const int64_t items = (int64_t)p.n_bundles * (128 / N);
+  const int64_t ctas = (items + kEncThreads / 32 - 1) / (kEncThreads / 32);
+  const int grid = (int)std::max<int64_t>(1, std::min<int64_t>(ctas, (int64_t)sm_count_current_device() * 8));
+  if (from_codes)
+    assemble_pages_kernel<3><<<grid, kEncThreads, smem_bytes, st>>>(a);
+  else
+    assemble_pages_kernel<2><<<grid, kEncThreads, smem_bytes, st>>>(a);
+  return check_launch("assemble_pages_kernel");
 }
 
 extern "C" int64_t sphkv_encode_scratch_bytes(int32_t n_pages, int32_t page_size, int32_t dh) {
@@ -642,26 +851,24 @@ static int encode_impl(const sphkv_encode_params* pp, void* stream, bool from_co
   const int64_t scratch_need = sphkv_encode_scratch_bytes(p.n_pages, p.page_size, p.dh);
   const bool split = p.scratch != nullptr && p.scratch_bytes >= scratch_need &&
                      ((uintptr_t)p.scratch & 15) == 0;
+  if (from_codes) return launch_assemble(a, true, st);
   {
-    static SmemOptIn opt_in[8];
-    const void* kernels[8] = {
-        (const void*)encode_bundle_kernel<16, 0>, (const void*)encode_bundle_kernel<16, 1>,
-        (const void*)encode_bundle_kernel<16, 2>, (const void*)encode_bundle_kernel<16, 3>,
-        (const void*)encode_bundle_kernel<32, 0>, (const void*)encode_bundle_kernel<32, 1>,
-        (const void*)encode_bundle_kernel<32, 2>, (const void*)encode_bundle_kernel<32, 3>};
-    for (int i = 0; i < 8; ++i)
+    static SmemOptIn opt_in[4];
+    const void* kernels[4] = {(const void*)encode_bundle_kernel<16, 0>, (const void*)encode_bundle_kernel<16, 1>,
+                              (const void*)encode_bundle_kernel<32, 0>, (const void*)encode_bundle_kernel<32, 1>};
+    for (int i = 0; i < 4; ++i)
       if (int rc = ensure_dynamic_smem(opt_in[i], kernels[i], smem_bytes, "encode")) return rc;
   }
-  // One launch per group size present; each skips the bundles of the other size.
+  // One search launch per group size present; each skips the bundles of the other size.
   bool any16 = false, any32 = false;
   for (int s = 0; s < p.tiers.n_slots; ++s) (p.tiers.g[s] == 16 ? any16 : any32) = true;
   if (any16) {
-    if (int rc = launch_encode<16>(a, split, from_codes, smem_bytes, st)) return rc;
+    if (int rc = launch_encode<16>(a, split, smem_bytes, st)) return rc;
   }
   if (any32) {
-    if (int rc = launch_encode<32>(a, split, from_codes, smem_bytes, st)) return rc;
+    if (int rc = launch_encode<32>(a, split, smem_bytes, st)) return rc;
   }
-  return 0;
+  return split ? launch_assemble(a, false, st) : 0;
 }
 
 extern "C" int sphkv_encode_pages(const sphkv_encode_params* p, void* stream) {
@@ -697,18 +904,34 @@ extern "C" int sphkv_encode_codes(const void* k_src, int32_t k_dtype, int64_t k_
       SPHKV_REQUIRE((a.r_out[s] == nullptr) == (a.th_out[s] == nullptr), SPHKV_E_ARG,
                     "encode_codes: slot %d needs both r_out and theta_out (or neither)", s);
       any = any || a.r_out[s] != nullptr;
+      SPHKV_REQUIRE((reinterpret_cast<uintptr_t>(a.r_out[s]) & 7) == 0 && (reinterpret_cast<uintptr_t>(a.th_out[s]) & 1) == 0,
+                    SPHKV_E_ARG, "encode_codes: slot %d outputs must be 8-byte (r) and 2-byte (theta) aligned", s);
       off += dh << tiers->bits[s];  // G_s * C_s * g_s floats
     }
   }
   SPHKV_REQUIRE(any, SPHKV_E_ARG, "encode_codes: no output requested");
-  const int smem_bytes = off * 4;
-  SPHKV_REQUIRE(smem_bytes <= 200 * 1024, SPHKV_E_LIMIT, "encode_codes: codebooks need %d B of shared memory", smem_bytes);
+  SPHKV_REQUIRE(off * 4 <= 200 * 1024, SPHKV_E_LIMIT, "encode_codes: codebooks need %d B of shared memory", off * 4);
+  // row blocks staged through shared memory when every 32-element slice starts on a 16-byte
+  // boundary and the blocks fit beside the codebooks
+  const int esz = k_dtype == SPHKV_F32 ? 4 : 2;
+  const int kbuf_bytes = (kCodeThreads / 32) * 32 * kCodeTok * 128;
+  const bool staged = (reinterpret_cast<uintptr_t>(k_src) & 15) == 0 && (k_row_stride * esz) % 16 == 0 &&
+                      (k_head_stride * esz) % 16 == 0 && (off * 4 + kbuf_bytes) * kCodeCtasPerSm <= 220 * 1024;
+  a.kbuf_off = off * 4;
+  const int smem_bytes = off * 4 + (staged ? kbuf_bytes : 0);
   {
-    static SmemOptIn opt_in;
-    if (int rc = ensure_dynamic_smem(opt_in, (const void*)encode_codes_kernel, smem_bytes, "encode_codes")) return rc;
+    static SmemOptIn opt_in[2];
+    const void* fn = staged ? (const void*)encode_codes_kernel<true> : (const void*)encode_codes_kernel<false>;
+    if (int rc = ensure_dynamic_smem(opt_in[staged], fn, smem_bytes, "encode_codes")) return rc;
   }
-  const int per_cta = (kEncThreads / 32) / (dh >> 5) * 32 * kCodeTok;  // rows per CTA
-  const dim3 grid((unsigned)((rows + per_cta - 1) / per_cta), (unsigned)Hkv);
-  encode_codes_kernel<<<grid, kEncThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  const int per_cta = (kCodeThreads / 32) / (dh >> 5) * 32 * kCodeTok;  // rows per CTA and pass
+  a.units_per_head = (rows + per_cta - 1) / per_cta;
+  a.n_units = a.units_per_head * Hkv;
+  const int64_t resident = (int64_t)sm_count_current_device() * kCodeCtasPerSm;  // CTAs that fit at once
+  const dim3 grid((unsigned)std::max<int64_t>(1, std::min(a.n_units, resident)));
+  if (staged)
+    encode_codes_kernel<true><<<grid, kCodeThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  else
+    encode_codes_kernel<false><<<grid, kCodeThreads, smem_bytes, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("encode_codes_kernel");
 }
