@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(kEncThreads) assemble_pages_kernel(const Encod
   const sphkv_encode_params& p = a.p;
   extern __shared__ __align__(16) uint8_t smem[];
   const int N = p.page_size, dh = p.dh, GST = dh >> 4;
-  const int ppb = 128 / N;
+  const int ppb_shift = __clz(N) - 24;  // log2 of the 128 / N pages per bundle (N is 16 .. 128)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* mine = smem + (size_t)warp * a.warp_smem_bytes;
   int* rows_w = reinterpret_cast<int*>(mine);
@@ -417,14 +417,16 @@ __global__ void __launch_bounds__(kEncThreads) assemble_pages_kernel(const Encod
   const float* scr_r = reinterpret_cast<const float*>(p.scratch);
   const uint8_t* scr_t = reinterpret_cast<const uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
-  const int64_t items = (int64_t)p.n_bundles * ppb;
+  const int64_t items = (int64_t)p.n_bundles << ppb_shift;
   for (int64_t it = (int64_t)blockIdx.x * (kEncThreads / 32) + warp; it < items; it += (int64_t)gridDim.x * (kEncThreads / 32)) {
-    const int page = p.bundles[8 * (it / ppb) + it % ppb];
+    const int page = p.bundles[8 * (it >> ppb_shift) + (it & ((1 << ppb_shift) - 1))];
     if (page < 0) continue;
     const int head = p.page_head[page], slot = p.page_slot[page];
     const int64_t poff = p.ptable[3 * (int64_t)page];
     const int gs = p.tiers.g[slot], bits = p.tiers.bits[slot];
     const int G = dh / gs, g_shift = 31 - __clz(G);
+    const float* code_r = SRC == 3 ? p.code_r[slot] + (int64_t)head * p.code_rows * G : nullptr;
+    const uint8_t* code_t = SRC == 3 ? p.code_theta[slot] + (int64_t)head * p.code_rows * G : nullptr;
     __syncwarp();  // the previous page's image has been copied out
     // ---- source rows and the valid-token count (valid slots form a prefix) -------------------
     int cnt = 0;
@@ -446,9 +448,8 @@ __global__ void __launch_bounds__(kEncThreads) assemble_pages_kernel(const Encod
       } else {
         const int row = rows_w[tin];
         if (row >= 0) {
-          const int64_t ci = ((int64_t)head * p.code_rows + row) * G + gq;
-          rv = p.code_r[slot][ci];
-          tv = p.code_theta[slot][ci];
+          rv = code_r[(int64_t)row * G + gq];
+          tv = code_t[(int64_t)row * G + gq];
         }
       }
       r_w[i] = rv;
@@ -618,22 +619,29 @@ __global__ void __launch_bounds__(kCodeThreads, kCodeCtasPerSm) encode_codes_ker
     const int64_t hd = uu / a.units_per_head;
     const int64_t c0 = hd * a.k_head_stride + grp * 32;
     const int64_t r0 = ((uu - hd * a.units_per_head) * sets + set) * kBlockRows;
-    const char* base = reinterpret_cast<const char*>(a.k_src);
-    if (k32) {
+    // lane -> (row lane / CH, chunk lane % CH) of every group of 32 / CH rows; one pointer walks the rows
+    const int esz = k32 ? 4 : 2, ch_shift = k32 ? 3 : 2, rows_per_i = 32 >> ch_shift;
+    const int r_l = lane >> ch_shift, c = lane & ((1 << ch_shift) - 1);
+    // chunk swizzle: row & 7 for 128-byte rows, (row >> 1) & 3 for 64-byte rows.  Eight 64-byte rows
+    // per step keep it fixed; four 128-byte rows per step flip bit 2 of it on odd steps.
+    const int sw = k32 ? r_l : ((r_l >> 1) & 3);
+    const char* src = reinterpret_cast<const char*>(a.k_src) + ((r0 + r_l) * a.k_row_stride + c0) * esz + c * 16;
+    const int64_t src_step = a.k_row_stride * esz * rows_per_i;
+    const uint32_t dst = kbuf + ((r_l << ch_shift) + (c ^ sw)) * 16;
+    const uint32_t dst_odd = k32 ? kbuf + ((r_l << ch_shift) + (c ^ sw ^ 4)) * 16 : dst;
+    const int64_t left = a.rows - r0 - r_l;  // rows of the block at or below this lane's first one
+    if (left >= kBlockRows) {
 #pragma unroll
-      for (int i = 0; i < kCodeTok * 8; ++i) {
-        const int f = i * 32 + lane, r = f >> 3, c = f & 7;
-        const bool in = r0 + r < a.rows;
-        cp_async_16_zfill(kbuf + r * 128 + ((c ^ (r & 7)) << 4),
-                          in ? base + ((r0 + r) * a.k_row_stride + c0) * 4 + c * 16 : base, in ? 16 : 0);
+      for (int i = 0; i < kBlockRows / 4; ++i) {
+        if (i < kBlockRows / rows_per_i) cp_async_16(((i & 1) ? dst_odd : dst) + i * 512, src + i * src_step);
       }
     } else {
 #pragma unroll
-      for (int i = 0; i < kCodeTok * 4; ++i) {
-        const int f = i * 32 + lane, r = f >> 2, c = f & 3;
-        const bool in = r0 + r < a.rows;
-        cp_async_16_zfill(kbuf + r * 64 + ((c ^ ((r >> 1) & 3)) << 4),
-                          in ? base + ((r0 + r) * a.k_row_stride + c0) * 2 + c * 16 : base, in ? 16 : 0);
+      for (int i = 0; i < kBlockRows / 4; ++i) {
+        if (i < kBlockRows / rows_per_i) {
+          const bool in = (int64_t)i * rows_per_i < left;
+          cp_async_16_zfill(((i & 1) ? dst_odd : dst) + i * 512, in ? src + i * src_step : reinterpret_cast<const char*>(a.k_src), in ? 16 : 0);
+        }
       }
     }
     cp_async_commit();

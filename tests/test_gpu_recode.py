@@ -17,17 +17,27 @@ def dev_lists(lists):
     return pkg.PageLists(**{k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in lists.__dict__.items()})
 
 
-@pytest.mark.parametrize("dh,T,k_dtype", [(128, 300, torch.float32), (64, 517, torch.float32),
-                                          (128, 131, torch.bfloat16), (128, 1, torch.float16)])
-def test_code_cache_equals_per_tier_encode(dh, T, k_dtype):
+@pytest.mark.parametrize("dh,T,k_dtype,shift", [(128, 300, torch.float32, 0), (64, 517, torch.float32, 0),
+                                                (128, 131, torch.bfloat16, 0), (128, 1, torch.float16, 0),
+                                                (128, 2900, torch.float32, 0), (64, 1500, torch.bfloat16, 0),
+                                                (128, 450, torch.float32, 1), (128, 450, torch.bfloat16, 3)])
+def test_code_cache_equals_per_tier_encode(dh, T, k_dtype, shift):
     """codes of all three reference tiers from one kernel == oracle.encode per tier, bit for bit
-    (radii as f32 bit patterns, centroid indices as bytes)"""
+    (radii as f32 bit patterns, centroid indices as bytes).  The long cases make a CTA walk several
+    row blocks and cross from one head to the next; shift > 0 puts the keys `shift` elements off a
+    16-byte boundary, which takes the kernel's direct-load route instead of the staged one."""
     Hkv, specs = 3, pkg.REFERENCE_TIERS
     tiers = pkg.TierSet(dh, specs)
     K, _, _, _ = synth.make_kvq(1, Hkv, Hkv, dh, T, seed=dh + T, outlier_frac=0.02)
     K = K.reshape(T, Hkv, dh).to(k_dtype)
     cbs = synth.make_codebooks(Hkv, dh, specs, seed=7)
-    codes = pkg.encode_codes(K.to(DEV), tiers.pack_codebooks(cbs).to(DEV), tiers)
+    Kd = K.to(DEV)
+    if shift:
+        flat = torch.empty(K.numel() + 8, dtype=k_dtype, device=DEV)
+        Kd = flat[shift:shift + K.numel()].view(T, Hkv, dh)
+        Kd.copy_(K)
+        assert Kd.data_ptr() % 16 != 0
+    codes = pkg.encode_codes(Kd, tiers.pack_codebooks(cbs).to(DEV), tiers)
     torch.cuda.synchronize()
     assert codes.rows == T
     for s, t in enumerate(specs):
