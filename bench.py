@@ -8,7 +8,11 @@ Prints ONE JSON line (rank 0).  `value` = microseconds per layer-step with the c
 resident in HBM (CUDA-graph replay of the 32 layer-steps); `e2e` = the same through the
 public API with the step's queries copied from pinned host memory and the outputs read back
 inside the timed region.  Under torchrun every rank owns its own batch rows (units are
-independent: no data-path collective), so per-GPU work is fixed ("weak").
+independent: no data-path collective), so per-GPU work is fixed ("weak").  The line also carries
+two blocks measured in the same run: `splitkv` (one 131072-token sequence cut over the N ranks, the
+exchange inside the merge kernel; T(1) on rank 0's GPU alongside) and `encode_c4` (32768 tokens x 8
+KV heads of fp32 keys: tier-1 and tier-2 codes from one pass, both page sets assembled from them);
+`--no-side` skips both.
 
 `--impl reference` times the CPU restatement of the reference's torch path
 (oracle/oracle.py) on a bounded sample of the same workload with all host threads.

@@ -17,7 +17,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "sphkv_ref_fused_decode"
-REF = os.environ.get("SPHKV_REFERENCE", "/root/reference")
+# the reference checkout: $SPHKV_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("SPHKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def built_path() -> str:

@@ -9,8 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# SPHKV_B200_LIB points at an alternative build of the same library (kernel experiments)
-LIB_PATH = os.environ.get("SPHKV_B200_LIB") or os.path.join(HERE, "libsphkv_b200.so")
+LIB_PATH = os.path.join(HERE, "libsphkv_b200.so")
 
 F32, BF16, F16 = 0, 1, 2
 RADIUS_I8, RADIUS_F16 = 0, 1

@@ -100,6 +100,13 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may
+// become resident while the kernel before it in the stream is still running; it must not touch
+// global memory until griddep_wait() returns (the predecessor has completed and its writes are
+// visible).  griddep_launch() lets the kernel after this one become resident in the same way.
+// Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }

@@ -297,6 +297,9 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __g
     fence_async_smem();
   }
   __syncthreads();
+  // everything above touched shared memory only: this grid's launch overlaps the tail of the kernel
+  // before it in the stream (the previous step's merge kernel, which lets it in early)
+  griddep_wait();
   // V ring position of the next tile to issue / to wait for: stage index and phase parity
   uint32_t vi_stage = 0, vw_stage = 0, vw_phase = 0;
   bool dead = false;  // a bounded wait ran out: stop working, keep meeting the CTA barriers
@@ -1079,6 +1082,10 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
   __shared__ int s_c[2];
   __shared__ float s_M[8], s_L[8];
   __shared__ float s_w[8][kChunk];
+  // The next kernel in the stream -- the next step's decode kernel -- may become resident now; it
+  // waits for this grid to complete before it touches global memory.  (Launching THIS kernel the
+  // same way measured 2 us slower per step, so it is launched plainly.)
+  griddep_launch();
   const int32_t* pfx = a.pfx;
   const int64_t T = pfx[a.n_units];
   const int64_t ps = pfx[u], pe = pfx[u + 1];
@@ -1389,12 +1396,31 @@ static int make_v_map(CUtensorMap* map, const sphkv_decode_params& p) {
   return 0;
 }
 
+// Launch with programmatic stream serialization: the grid may become resident while the kernel
+// before it in the stream is still running.  Only for kernels that call griddep_wait() before
+// their first global-memory access.
+template <typename Arg>
+static cudaError_t launch_after_predecessor_starts(void (*kern)(Arg), dim3 grid, dim3 block, size_t smem_bytes,
+                                                   cudaStream_t st, const DecodeArgs& a) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
 template <int DH, typename VT, bool ROT, int MODE, bool PACK>
 static int launch_decode_t(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   static SmemOptIn opt_in;
   auto kern = decode_splitk_kernel<DH, VT, ROT, MODE, PACK>;
   if (int rc = ensure_dynamic_smem(opt_in, (const void*)kern, smem_bytes, "decode")) return rc;
-  kern<<<a.n_ctas, kWarps * 32, smem_bytes, st>>>(a);
+  (void)launch_after_predecessor_starts(kern, dim3(a.n_ctas), dim3(kWarps * 32), smem_bytes, st, a);  // check_launch reports
   return check_launch("decode_splitk_kernel");
 }
 

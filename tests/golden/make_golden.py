@@ -1,5 +1,5 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE
-(Anay21013/Spherical-KV, expected at /root/reference or $SPHKV_REFERENCE) on seeded inputs.
+(Anay21013/Spherical-KV, expected at $SPHKV_REFERENCE or in a directory "reference" beside this repository) on seeded inputs.
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py
 
@@ -27,7 +27,8 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("SPHKV_REFERENCE", "/root/reference")
+# the reference checkout: $SPHKV_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("SPHKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 sys.path.insert(0, ROOT)
 sys.dont_write_bytecode = True
 pkg = importlib.import_module("spherical-kv_b200")

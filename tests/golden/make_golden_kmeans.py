@@ -17,7 +17,8 @@ import torch
 import torch.nn.functional as F
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("SPHKV_REFERENCE", "/root/reference")
+# the reference checkout: $SPHKV_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("SPHKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 sys.dont_write_bytecode = True
 
 

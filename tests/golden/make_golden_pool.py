@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("SPHKV_REFERENCE", "/root/reference")
+# the reference checkout: $SPHKV_REFERENCE, else a directory named "reference" beside this repository
+REF = os.environ.get("SPHKV_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 sys.dont_write_bytecode = True
 
 NUM_KV, KV_GROUPS, DH, PAGE, CAPACITY, STEPS = 2, 2, 128, 16, 8, 20

@@ -193,3 +193,34 @@ def test_capacity_exhaustion_sets_flag_and_writes_nothing(lut):
     assert st[3] == 1 and st[2] == 0 and st[0] == int(before[6][0])
     with pytest.raises(RuntimeError, match="capacity"):
         pool.check_overflow()
+
+
+REF_DIR = os.environ.get("SPHKV_REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+@pytest.mark.skipif(not os.path.exists(os.path.join(REF_DIR, "sphkv_lut.py")),
+                    reason="needs a checkout of the reference next to this repository (or $SPHKV_REFERENCE)")
+def test_reference_own_layerpool_runs_on_the_dropin_kernels(lut):
+    """The reference's sphkv_lut.LayerPool, unmodified, with only its `fused_decode` import
+    resolved to this package's drop-in module: construction and 20 steps agree with the
+    device-resident LayerPool (which the other tests pin to the golden fixture)."""
+    import importlib.util
+    sys.path.insert(0, DROPIN)
+    import fused_decode as dropin_fd                                  # noqa: F401  (the drop-in, first on the path)
+    assert os.path.dirname(os.path.abspath(dropin_fd.__file__)) == DROPIN
+    sys.path.append(REF_DIR)                                          # codebook_loader comes from the reference
+    spec = importlib.util.spec_from_file_location("sphkv_lut_reference", os.path.join(REF_DIR, "sphkv_lut.py"))
+    ref_lut = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_lut)
+    z, pool, tiers, shp = golden_pool(lut)
+    _, ref_pool, _, _ = golden_pool(ref_lut)
+    for name in ("theta_codes", "radius_codes", "r_scales", "v_pool", "block_table_gpu", "bits_table_gpu",
+                 "ctx_lens_gpu", "cb_flat"):
+        assert torch.equal(getattr(pool, name), getattr(ref_pool, name)), name
+    outs, _ = run_steps(pool, tiers, shp, 20, seed=5)
+    ref_outs, _ = run_steps(ref_pool, tiers, shp, 20, seed=5)
+    torch.cuda.synchronize()
+    for a, b in zip(outs, ref_outs):
+        assert torch.equal(a, b)
+    for name in ("theta_codes", "radius_codes", "r_scales", "v_pool", "ctx_lens_gpu"):
+        assert torch.equal(getattr(pool, name), getattr(ref_pool, name)), name
