@@ -37,7 +37,7 @@ import torch  # noqa: E402
 CFG = dict(B=8, Hq=32, Hkv=8, dh=128, ctx=32768, layers=32, page_size=16)
 METRIC, UNIT = "decode_attn_us_per_layer_step", "us"
 # measured DRAM bytes / algorithmic bytes of the decode kernel (profiles/decode_splitk_ctx16k_ncu.txt)
-DRAM_TRAFFIC_RATIO = 1.089
+DRAM_TRAFFIC_RATIO = 1.080
 
 
 def algorithmic_bytes(lists, tiers, dh: int) -> float:
@@ -823,7 +823,7 @@ def main() -> None:
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": alg_bytes * DRAM_TRAFFIC_RATIO, "peak_source": peak_src,
                          "traffic_source": "ncu dram__bytes_read+write of one decode launch on a ctx-16384 case "
-                                           "(292.5 MB for 268.7 MB algorithmic), scaled by token-heads",
+                                           "(290.2 MB for 268.7 MB algorithmic), scaled by token-heads",
                          "algorithmic_bytes_per_launch": alg_bytes,
                          "note": "duration = one layer-step (decode + merge kernels) from CUDA "
                                  "events over the timed region; frac_of_8TBs = %.3f" % (achieved / 8000.0)},

@@ -263,12 +263,12 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 
 // PACK (<= 4 query heads per KV head): the 8 mma columns carry [q_hi heads 0..3 | q_lo heads
 // 0..3] (one product fewer per step) and later [P_hi | P_lo] (one product per V tile).
-// MODE 0: 16-token pages with int8 radii and no side outputs (the serving configuration: page
-// size and radius format are compile-time constants); 1: any page size / radius format;
-// 2: as 1, plus the logits / per-tile statistics side outputs.
+// MODE bit 0 clear: 16-token pages with int8 radii (the serving configuration: page size and
+// radius format are compile-time constants and the page image is staged word for word); set: any
+// page size / radius format.  MODE bit 1: the logits / per-tile statistics side outputs.
 template <int DH, typename VT, bool ROT, int MODE, bool PACK>
 __global__ void __launch_bounds__(kWarps * 32, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
-  constexpr bool EXTRA = MODE == 2, FAST = MODE == 0;
+  constexpr bool EXTRA = (MODE & 2) != 0, FAST = (MODE & 1) == 0;
   constexpr int KS = DH / 16;   // 16-dim output tiles of the V product
   constexpr int W = DH / 8;     // dims a lane owns in each rotary half
   constexpr int NCH = W / 4;    // 16-byte chunks of those dims
@@ -1428,9 +1428,14 @@ template <int DH, typename VT, bool ROT>
 static int launch_decode_r(const DecodeArgs& a, int smem_bytes, cudaStream_t st) {
   const bool extra = a.p.logits_out != nullptr || a.p.page_ml != nullptr;
   const bool pack = a.grp <= 4;
-  if (extra) return pack ? launch_decode_t<DH, VT, ROT, 2, true>(a, smem_bytes, st)
-                         : launch_decode_t<DH, VT, ROT, 2, false>(a, smem_bytes, st);
-  if (a.p.page_size == 16 && a.p.radius_fmt == SPHKV_RADIUS_I8)
+  const bool fast = a.p.page_size == 16 && a.p.radius_fmt == SPHKV_RADIUS_I8;
+  if (extra && fast)
+    return pack ? launch_decode_t<DH, VT, ROT, 2, true>(a, smem_bytes, st)
+                : launch_decode_t<DH, VT, ROT, 2, false>(a, smem_bytes, st);
+  if (extra)
+    return pack ? launch_decode_t<DH, VT, ROT, 3, true>(a, smem_bytes, st)
+                : launch_decode_t<DH, VT, ROT, 3, false>(a, smem_bytes, st);
+  if (fast)
     return pack ? launch_decode_t<DH, VT, ROT, 0, true>(a, smem_bytes, st)
                 : launch_decode_t<DH, VT, ROT, 0, false>(a, smem_bytes, st);
   return pack ? launch_decode_t<DH, VT, ROT, 1, true>(a, smem_bytes, st)
