@@ -481,14 +481,14 @@ __global__ void __launch_bounds__(kEncThreads) assemble_pages_kernel(const Encod
       if (lane < G) reinterpret_cast<float*>(img + 8)[lane] = scale_w[lane];
       for (int w = lane; w < th_words; w += 32) {
         const int bit0 = w * 32;
-        int i = bit0 / bits;  // first value overlapping this word
-        uint32_t acc = 0;
-        for (; i < nvals && i * bits < bit0 + 32; ++i) {
-          const uint32_t v = th_w[i];
-          const int sh = i * bits - bit0;
-          acc |= sh >= 0 ? (v << sh) : (v >> (-sh));
-        }
-        reinterpret_cast<uint32_t*>(img + hdr)[w] = acc;
+        const int i0 = bit0 / bits;                             // first value overlapping this word
+        const int i1 = min(nvals, (bit0 + 31) / bits + 1);      // one past the last
+        // values enter a 64-bit window that starts 8 bits below the word, so a value that begins
+        // in the previous word (bits <= 8) needs no right shift
+        int sh = i0 * bits - bit0 + 8;
+        unsigned long long acc = 0;
+        for (int i = i0; i < i1; ++i, sh += bits) acc |= (unsigned long long)th_w[i] << sh;
+        reinterpret_cast<uint32_t*>(img + hdr)[w] = (uint32_t)(acc >> 8);
       }
       __syncwarp();
       // ---- radii (may overlay the zero tail of the last theta word) ---------------------------
