@@ -586,6 +586,14 @@ def splitkv_block(args, pkg, dev, rank, world):
             pkg.decode_paged(q, c, rope, out=o, exchange=ex)
 
     tn_us = _graph_time(split_step, args.steps, args.warmup, dev, world) * 1e3 / n_seq
+    # the same shards decoded without the exchange (partial rows only): what a rank spends on its own
+    parts = [torch.empty(1, Hq, dh + 2, device=dev) for _ in range(n_seq)]
+
+    def local_step():
+        for c, q, pt in zip(shards, qs, parts):
+            pkg.decode_paged(q, c, rope, out_partial=pt, want_out=False)
+
+    local_us = _graph_time(local_step, args.steps, args.warmup, dev, world) * 1e3 / n_seq
     torch.cuda.synchronize()
     diff = max(float((a.float() - b.float()).abs().max()) for a, b in zip(out_split, out_full))
     status = sum(int(c.status.item()) for c in shards)
@@ -593,6 +601,7 @@ def splitkv_block(args, pkg, dev, rank, world):
     import torch.distributed as dist
     dist.all_reduce(st, op=dist.ReduceOp.MAX)
     blk.update({"us_per_step": tn_us, "efficiency": t1_us / (world * tn_us),
+                "local_us_per_step": local_us, "exchange_us_per_step": tn_us - local_us,
                 "exchange": "peer stores + sequence flags + bounded wait inside the merge kernel (no collective)",
                 "bytes_sent_per_rank_per_step": (world - 1) * Hq * (dh + 2) * 4,
                 "merged_vs_single_pass_max_abs": float(st[0].item()), "kernel_status": int(st[1].item()),

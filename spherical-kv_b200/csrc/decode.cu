@@ -1180,10 +1180,20 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
       const int i = threadIdx.x + q * 256;
       const int n = i / DH, d = i - n * DH;
       if (n < a.grp) {
+        // eight rows' loads in flight at a time (a unit cut over many CTAs has tens of rows: one
+        // dependent load per row made this loop the whole kernel); a row that does not exist has
+        // weight 0 and whatever the scratch holds there is discarded by the select
         float o = o_acc[q];
-        for (int ci = 0; ci < nc; ++ci) {
-          const float w = s_w[n][ci];
-          if (w != 0.f) o += w * a.rows[((int64_t)(c_lo + c0 + ci + u) * 8 + n) * (DH + 2) + 2 + d];
+        const float* col = a.rows + ((int64_t)(c_lo + c0 + u) * 8 + n) * (DH + 2) + 2 + d;
+        for (int ci = 0; ci < nc; ci += 8) {
+          float v[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = ci + k < nc ? col[(int64_t)(ci + k) * 8 * (DH + 2)] : 0.f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float w = ci + k < nc ? s_w[n][ci + k] : 0.f;
+            o += w != 0.f ? w * v[k] : 0.f;
+          }
         }
         o_acc[q] = o;
       }
