@@ -602,8 +602,9 @@ def splitkv_block(args, pkg, dev, rank, world):
     dist.all_reduce(st, op=dist.ReduceOp.MAX)
     blk.update({"us_per_step": tn_us, "efficiency": t1_us / (world * tn_us),
                 "local_us_per_step": local_us, "exchange_us_per_step": tn_us - local_us,
-                "exchange": "peer stores + sequence flags + bounded wait inside the merge kernel (no collective)",
-                "bytes_sent_per_rank_per_step": (world - 1) * Hq * (dh + 2) * 4,
+                "exchange": "peer stores of 64-bit (step, value) words + bounded wait inside the merge kernel "
+                            "(no fence, flag or collective)",
+                "bytes_sent_per_rank_per_step": (world - 1) * Hq * (dh + 2) * 8,
                 "merged_vs_single_pass_max_abs": float(st[0].item()), "kernel_status": int(st[1].item()),
                 "achieved_hbm_gbs_all_gpus": alg / (tn_us * 1e-6) / 1e9})
     ex.close()

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define SPHKV_ABI_VERSION 3
+#define SPHKV_ABI_VERSION 4
 
 /* error codes */
 #define SPHKV_OK 0
@@ -182,23 +182,22 @@ typedef struct sphkv_decode_params {
   /* Cross-GPU split-KV exchange inside the merge kernel (xchg_world <= 1: off).  The block
    * tables of this call cover this rank's share of every sequence; the un-normalised
    * (max, sum, acc) rows of every (batch row, query head) are stored straight into every
-   * rank's receive buffer (plain peer stores over NVLink), a per-(rank, unit) sequence flag is
-   * released, and the same kernel waits -- bounded -- for the flags of all ranks, combines the
-   * `xchg_world` partial sets by log-sum-exp (math of decode_kernel.cu:230-245) and writes
-   * `out`.  No collective library call, no extra launch.
-   *   xchg_recv[q]  : rank q's receive buffer in rank q's memory, f32
-   *                   [2][xchg_world][B*Hq][dh+2] (two slots alternate by step)
-   *   xchg_flags[q] : rank q's flags, i32 [2][xchg_world][B*Hkv] (one set per slot),
- *                   zero-initialised once
+   * rank's receive buffer (plain peer stores over NVLink) as 64-bit words that carry the step
+   * number beside the value, (seq << 32) | f32 bits, so every word validates itself: no fence,
+   * no flag, no collective library call, no extra launch.  The same kernel then waits --
+   * bounded -- until the words of all ranks carry this step's number, combines the `xchg_world`
+   * partial sets by log-sum-exp (math of decode_kernel.cu:230-245) and writes `out`.
+   *   xchg_recv[q]  : rank q's receive buffer in rank q's memory, u64
+   *                   [2][xchg_world][B*Hq][dh+2] (two slots alternate by step),
+   *                   zero-initialised once
    *   xchg_seq      : this rank's step counters, i32 [B*Hkv], zero-initialised once; every
    *                   call advances them by one, so calls replay from a CUDA graph
-   * Both pointer arrays live in device memory of this rank and hold xchg_world entries (entry
-   * xchg_rank = this rank's own buffers).  All ranks must issue the same sequence of calls.  A
+   * The pointer array lives in device memory of this rank and holds xchg_world entries (entry
+   * xchg_rank = this rank's own buffer).  All ranks must issue the same sequence of calls.  A
    * wait that exceeds xchg_timeout_cycles SM clocks (0 = 2e9, about a second) gives up: the
-   * kernel raises SPHKV_ST_TIMEOUT in `status`, writes zeros to the rows it could not
-   * complete and returns. */
-  float* const* xchg_recv;
-  int32_t* const* xchg_flags;
+   * kernel raises SPHKV_ST_TIMEOUT in `status`, writes zeros to the rows of that unit and
+   * returns. */
+  unsigned long long* const* xchg_recv;
   int32_t* xchg_seq;
   int64_t xchg_timeout_cycles;
   int32_t xchg_rank, xchg_world;
@@ -230,7 +229,7 @@ int sphkv_decode_paged(const sphkv_decode_params* p, void* stream);
  * host threads -- race on it and must be serialised by the caller. */
 int sphkv_decode_paged_static(const sphkv_decode_params* p, void* stream);
 
-/* Buffers of the split-KV peer exchange (xchg_recv / xchg_flags of sphkv_decode_params); no
+/* Buffers of the split-KV peer exchange (xchg_recv of sphkv_decode_params); no
  * counterpart in the reference, which has no multi-GPU path.  They are written by kernels of
  * other GPUs, each driven by its own process, so they travel as CUDA IPC handles:
  *   sphkv_xchg_alloc  cudaMalloc + zero fill on the current device; returns the pointer and the

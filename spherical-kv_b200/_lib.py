@@ -56,7 +56,7 @@ class DecodeParams(C.Structure):
         ("q_dtype", C.c_int32), ("v_dtype", C.c_int32), ("out_dtype", C.c_int32),
         ("radius_fmt", C.c_int32), ("n_ctas", C.c_int32), ("sm_scale", C.c_float),
         ("ema_beta", C.c_float), ("tiers", Tiers),
-        ("xchg_recv", C.c_void_p), ("xchg_flags", C.c_void_p), ("xchg_seq", C.c_void_p),
+        ("xchg_recv", C.c_void_p), ("xchg_seq", C.c_void_p),
         ("xchg_timeout_cycles", C.c_int64), ("xchg_rank", C.c_int32), ("xchg_world", C.c_int32),
     ]
 
@@ -119,8 +119,8 @@ def load() -> C.CDLL:
         fn.restype = res
         fn.argtypes = args
     ver = lib.sphkv_abi_version()
-    if ver != 3:
-        raise SphKVError(f"libsphkv_b200.so ABI version {ver}, expected 3")
+    if ver != 4:
+        raise SphKVError(f"libsphkv_b200.so ABI version {ver}, expected 4")
     for which, st in enumerate((Tiers, EncodeParams, DecodeParams)):
         if lib.sphkv_struct_size(which) != C.sizeof(st):
             raise SphKVError(f"struct layout mismatch for {st.__name__}: library "

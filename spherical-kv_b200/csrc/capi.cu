@@ -70,7 +70,7 @@ extern "C" int sphkv_struct_size(int which) {
 }
 
 // ---- exchange buffers for split-KV across the GPUs of one node ---------------------------------
-// The receive buffers and flags of the peer exchange are written by kernels that run on OTHER
+// The receive buffers of the peer exchange are written by kernels that run on OTHER
 // GPUs, each in its own process.  They are allocated here with cudaMalloc (one allocation = one
 // IPC handle, no sub-allocation offsets to carry around) and opened by the other ranks with the
 // opening rank's device current, which is what maps the memory into that device's address space

@@ -1221,16 +1221,25 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
   if (p.xchg_world <= 1) return;
 
   // ---- split-KV exchange: this rank's rows of the unit go to every rank, then the unit is
-  //      combined over the ranks here.  Peer memory is touched by plain stores only.
+  //      combined over the ranks here.  Every 64-bit word a rank stores carries the step number
+  //      beside the value ((seq << 32) | f32 bits, one single-copy-atomic store), so a word
+  //      validates itself: no fence, no separate flag, one NVLink crossing per value.  Peer
+  //      memory is touched by plain stores only; the words a rank reads are in its own memory.
   __shared__ int s_seq, s_ok;
   __shared__ float s_rm[SPHKV_MAX_XCHG_RANKS][8], s_rl[SPHKV_MAX_XCHG_RANKS][8];
   const int unit = b * p.Hkv + hkv;
-  const int n_units = p.B * p.Hkv;
   const int64_t n_rows = (int64_t)p.B * p.Hq;
-  if (threadIdx.x == 0) s_seq = p.xchg_seq[unit] + 1;
+  if (threadIdx.x == 0) {
+    s_seq = p.xchg_seq[unit] + 1;
+    s_ok = 1;
+  }
   __syncthreads();
-  const int seq = s_seq;
-  const int64_t slot_base = (int64_t)(seq & 1) * p.xchg_world * n_rows;  // rows
+  const uint32_t seq = (uint32_t)s_seq;
+  const int64_t slot_base = (int64_t)(seq & 1) * p.xchg_world * n_rows;  // rows; the two slots alternate by step
+  auto put = [&](unsigned long long* dst, float v) {
+    const unsigned long long w = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(dst), "l"(w) : "memory");
+  };
 #pragma unroll
   for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
     const int i = threadIdx.x + q * 256;
@@ -1239,70 +1248,73 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
     const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
     const int64_t off = (slot_base + (int64_t)p.xchg_rank * n_rows + hq) * (DH + 2);
     for (int peer = 0; peer < p.xchg_world; ++peer) {
-      float* dst = p.xchg_recv[peer] + off;
+      unsigned long long* dst = p.xchg_recv[peer] + off;
       if (d == 0) {
-        dst[0] = s_M[n] * kLn2;
-        dst[1] = s_L[n];
+        put(dst, s_M[n] * kLn2);
+        put(dst + 1, s_L[n]);
       }
-      dst[2 + d] = o_acc[q];
+      put(dst + 2 + d, o_acc[q]);
     }
   }
-  __threadfence_system();  // the rows are visible system-wide before the flag is
-  __syncthreads();
-  if (threadIdx.x < p.xchg_world) {
-    int32_t* flag = p.xchg_flags[threadIdx.x] + ((int64_t)(seq & 1) * p.xchg_world + p.xchg_rank) * n_units + unit;
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(seq) : "memory");
-  }
-  // bounded wait for every rank's flag of this unit and step
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  if (threadIdx.x < p.xchg_world) {
-    const int32_t* flag = p.xchg_flags[p.xchg_rank] + ((int64_t)(seq & 1) * p.xchg_world + threadIdx.x) * n_units + unit;
-    const long long limit = p.xchg_timeout_cycles > 0 ? p.xchg_timeout_cycles : 2000000000LL;
-    const long long t0 = clock64();
-    int seen;
+  // Bounded wait, word by word: a word of this step's slot is in when it carries exactly this
+  // step's number (a later step of a peer goes to the other slot; a peer cannot be two steps
+  // ahead because it needs this rank's next step to finish its own).  The wait also runs when
+  // no output is wanted: it is what keeps the ranks within one step of each other.
+  const unsigned long long* mine = p.xchg_recv[p.xchg_rank] + slot_base * (DH + 2);
+  const long long limit = p.xchg_timeout_cycles > 0 ? p.xchg_timeout_cycles : 2000000000LL;
+  const long long t0 = clock64();
+  auto get = [&](const unsigned long long* src) -> float {
     for (;;) {
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-      if (seen == seq) break;  // the flag of this slot: a later step of the peer uses the other slot
-      if (clock64() - t0 > limit) { s_ok = 0; break; }
+      unsigned long long w;
+      asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(src) : "memory");
+      if ((uint32_t)(w >> 32) == seq) return __uint_as_float((uint32_t)w);
+      if (clock64() - t0 > limit) {
+        s_ok = 0;  // every thread that gives up writes the same value
+        return 0.f;
+      }
     }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) p.xchg_seq[unit] = seq;
-  if (!s_ok) {
-    // a rank never published this step: report it and leave defined output
-    if (threadIdx.x == 0 && p.status) atomicOr(p.status, SPHKV_ST_TIMEOUT);
-    if (p.out != nullptr)
-      for (int i = threadIdx.x; i < a.grp * DH; i += blockDim.x)
-        store_from_float(p.out, p.out_dtype, ((int64_t)b * p.Hq + (int64_t)hkv * a.grp) * DH + i, 0.f);
-    return;
-  }
-  const float* mine = p.xchg_recv[p.xchg_rank] + slot_base * (DH + 2);
+  };
   for (int i = threadIdx.x; i < p.xchg_world * a.grp; i += blockDim.x) {
     const int rr = i / a.grp, n = i - rr * a.grp;
     const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
-    const float* pr = mine + ((int64_t)rr * n_rows + hq) * (DH + 2);
-    // the rows were written by other GPUs: read them past L1, which is not coherent with them
-    const float pm = __ldcg(pr), pl = __ldcg(pr + 1);
+    const unsigned long long* pr = mine + ((int64_t)rr * n_rows + hq) * (DH + 2);
+    const float pm = get(pr), pl = get(pr + 1);
     s_rm[rr][n] = pl > 0.f ? pm : -INFINITY;
     s_rl[rr][n] = pl;
   }
   __syncthreads();
-  if (p.out == nullptr) return;
-  for (int i = threadIdx.x; i < a.grp * DH; i += blockDim.x) {
+  float res[(8 * DH + 255) / 256];
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+    const int i = threadIdx.x + q * 256;
     const int n = i / DH, d = i - n * DH;
+    res[q] = 0.f;
+    if (n >= a.grp) continue;
     const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
     float M = -INFINITY;
     for (int rr = 0; rr < p.xchg_world; ++rr) M = fmaxf(M, s_rm[rr][n]);
     float l = 0.f, o = 0.f;
-    if (M != -INFINITY)
-      for (int rr = 0; rr < p.xchg_world; ++rr) {
-        if (s_rm[rr][n] == -INFINITY) continue;
-        const float w = __expf(s_rm[rr][n] - M);
-        l += s_rl[rr][n] * w;
-        o += __ldcg(mine + ((int64_t)rr * n_rows + hq) * (DH + 2) + 2 + d) * w;
-      }
-    store_from_float(p.out, p.out_dtype, hq * DH + d, l > 0.f ? o / l : 0.f);
+    for (int rr = 0; rr < p.xchg_world; ++rr) {
+      const float v = get(mine + ((int64_t)rr * n_rows + hq) * (DH + 2) + 2 + d);  // every word is awaited
+      if (M == -INFINITY || s_rm[rr][n] == -INFINITY) continue;
+      const float w = __expf(s_rm[rr][n] - M);
+      l += s_rl[rr][n] * w;
+      o += v * w;
+    }
+    res[q] = l > 0.f ? o / l : 0.f;
+  }
+  __syncthreads();  // every wait has ended, one way or the other
+  if (threadIdx.x == 0) p.xchg_seq[unit] = (int32_t)seq;
+  const bool ok = s_ok != 0;
+  if (!ok && threadIdx.x == 0 && p.status) atomicOr(p.status, SPHKV_ST_TIMEOUT);  // a rank never published this step
+  if (p.out == nullptr) return;
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+    const int i = threadIdx.x + q * 256;
+    const int n = i / DH, d = i - n * DH;
+    if (n >= a.grp) continue;
+    const int64_t hq = (int64_t)b * p.Hq + (int64_t)hkv * a.grp + n;
+    store_from_float(p.out, p.out_dtype, hq * DH + d, ok ? res[q] : 0.f);  // defined output either way
   }
 }
 
@@ -1523,8 +1535,7 @@ extern "C" int sphkv_decode_paged(const sphkv_decode_params* pp, void* stream) {
                   p.xchg_world, SPHKV_MAX_XCHG_RANKS);
     SPHKV_REQUIRE(p.xchg_rank >= 0 && p.xchg_rank < p.xchg_world, SPHKV_E_ARG, "decode: xchg_rank=%d of %d",
                   p.xchg_rank, p.xchg_world);
-    SPHKV_REQUIRE(p.xchg_recv && p.xchg_flags && p.xchg_seq, SPHKV_E_ARG,
-                  "decode: the exchange needs xchg_recv, xchg_flags and xchg_seq");
+    SPHKV_REQUIRE(p.xchg_recv && p.xchg_seq, SPHKV_E_ARG, "decode: the exchange needs xchg_recv and xchg_seq");
     SPHKV_REQUIRE(p.omega == nullptr, SPHKV_E_ARG,
                   "decode: the page-importance update is per rank; run it without the exchange");
   }

@@ -230,7 +230,7 @@ def decode_paged(q: torch.Tensor, cache: PagedCache, rope: Optional[torch.Tensor
     p.tiers = cache.tiers.to_c()
     if exchange is not None and exchange.world > 1:
         exchange.check_shape(B, Hq, L.Hkv, dh)
-        p.xchg_recv, p.xchg_flags = exchange.recv_ptrs.data_ptr(), exchange.flag_ptrs.data_ptr()
+        p.xchg_recv = exchange.recv_ptrs.data_ptr()
         p.xchg_seq, p.xchg_timeout_cycles = exchange.seq.data_ptr(), exchange.timeout_cycles
         p.xchg_rank, p.xchg_world = exchange.rank, exchange.world
     _lib.check(lib.sphkv_decode_paged(C.byref(p), _stream()), "sphkv_decode_paged")

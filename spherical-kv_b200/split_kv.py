@@ -7,11 +7,12 @@ its single-GPU analogue is the per-page partial + sphkv_reduce_kernel (decode_ke
 Two exchanges, one process per GPU either way:
 
 * `PeerExchange` (GPUs of one node): the merge kernel itself stores this rank's rows into every
-  rank's receive buffer with plain peer stores over NVLink, releases a per-(rank, unit) sequence
-  flag and waits -- bounded -- for the other ranks' flags before it combines.  A decode step is
-  the two launches of a single-GPU step; nothing is sent through a collective library, and the
-  step replays from a CUDA graph (the sequence numbers live in device memory).  torch.distributed
-  is used once, at set-up, to swap the CUDA IPC handles of the buffers.
+  rank's receive buffer with plain peer stores over NVLink -- 64-bit words that carry the step
+  number beside the value, so a word validates itself and neither a fence nor a flag is needed --
+  and waits, bounded, until the words of all ranks carry this step's number before it combines.
+  A decode step is the two launches of a single-GPU step; nothing is sent through a collective
+  library, and the step replays from a CUDA graph (the step numbers live in device memory).
+  torch.distributed is used once, at set-up, to swap the CUDA IPC handles of the buffers.
 * `SplitKVDecoder` without a PeerExchange: an all-gather (NCCL on GPUs, gloo on CPUs in the
   tests) followed by the merge kernel; the portable path.
 """
@@ -35,8 +36,8 @@ def shard_cache(cache: PagedCache, rank: int, world: int) -> PagedCache:
 
 class ExchangeState:
     """Bookkeeping of the peer exchange that needs no GPU: which of the two receive slots a step
-    uses and where a rank's rows and flags sit.  Mirrors the index arithmetic of the merge
-    kernel so that it can be checked on CPUs."""
+    uses, where a rank's rows sit and how a word is packed.  Mirrors the index arithmetic of the
+    merge kernel so that it can be checked on CPUs."""
 
     def __init__(self, rank: int, world: int, B: int, Hq: int, Hkv: int, dh: int):
         if not 0 <= rank < world:
@@ -46,11 +47,8 @@ class ExchangeState:
 
     @property
     def recv_numel(self) -> int:
+        """64-bit words of one receive buffer."""
         return 2 * self.world * self.rows * (self.dh + 2)
-
-    @property
-    def flags_numel(self) -> int:
-        return 2 * self.world * self.units
 
     def slot(self, seq: int) -> int:
         """Receive slot of step `seq` (steps count from 1): the two slots alternate, so a rank
@@ -58,25 +56,33 @@ class ExchangeState:
         return seq & 1
 
     def row_offset(self, seq: int, src_rank: int, row: int) -> int:
-        """Element offset in a receive buffer of row `row` written by `src_rank` in step `seq`."""
+        """Word offset in a receive buffer of row `row` written by `src_rank` in step `seq`."""
         return ((self.slot(seq) * self.world + src_rank) * self.rows + row) * (self.dh + 2)
 
-    def flag_offset(self, seq: int, src_rank: int, unit: int) -> int:
-        """Element offset of the flag `src_rank` releases for `unit` in step `seq`: flags are per
-        slot like the rows, so a rank that is already in the next step does not disturb it."""
-        return (self.slot(seq) * self.world + src_rank) * self.units + unit
+    @staticmethod
+    def pack(values: torch.Tensor, seq: int) -> torch.Tensor:
+        """f32 values -> i64 words `(seq << 32) | bits(value)`, what the kernel stores."""
+        bits = values.detach().contiguous().float().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+        return bits | (int(seq) << 32)
 
     @staticmethod
-    def arrived(flag_value: int, seq: int) -> bool:
-        """Step `seq` of a peer is in when the flag of that step's slot holds exactly `seq`: a
-        rank that skipped the step never writes it."""
-        return flag_value == seq
+    def unpack(words: torch.Tensor):
+        """i64 words -> (f32 values, i64 step numbers)."""
+        lo = (words & 0xFFFFFFFF).to(torch.int64)
+        lo = torch.where(lo >= 2 ** 31, lo - 2 ** 32, lo).to(torch.int32)
+        return lo.view(torch.float32), words >> 32
+
+    @staticmethod
+    def arrived(word_seq: int, seq: int) -> bool:
+        """A word of step `seq`'s slot is in when it carries exactly `seq`: a rank that skipped
+        the step never writes it, and what an earlier step left there is not mistaken for it."""
+        return word_seq == seq
 
 
 class PeerExchange(ExchangeState):
-    """Receive buffers, flags and step counters of one rank plus the peers' device pointers.
+    """Receive buffer and step counters of one rank plus the peers' device pointers.
 
-    Every rank allocates its two buffers through the library (plain cudaMalloc: one allocation,
+    Every rank allocates its buffer through the library (plain cudaMalloc: one allocation,
     one IPC handle), the 64-byte handles travel once through `group`, and every rank opens the
     others' buffers with its own device current -- that is what maps them into this GPU's
     address space and enables peer access -- then uploads the pointer arrays the kernel reads.
@@ -96,29 +102,24 @@ class PeerExchange(ExchangeState):
         lib = _lib.load()
         self._own, self._opened = [], []
         with torch.cuda.device(dev):
-            handles = []
-            for nbytes in (self.recv_numel * 4, self.flags_numel * 4):
-                ptr, h = C.c_void_p(), C.create_string_buffer(64)
-                _lib.check(lib.sphkv_xchg_alloc(nbytes, C.byref(ptr), h), "sphkv_xchg_alloc")
-                self._own.append(ptr.value)
-                handles.append(h.raw)
-            recv_ptrs, flag_ptrs = [0] * world, [0] * world
-            recv_ptrs[rank], flag_ptrs[rank] = self._own
+            ptr, h = C.c_void_p(), C.create_string_buffer(64)
+            _lib.check(lib.sphkv_xchg_alloc(self.recv_numel * 8, C.byref(ptr), h), "sphkv_xchg_alloc")
+            self._own.append(ptr.value)
+            recv_ptrs = [0] * world
+            recv_ptrs[rank] = ptr.value
             if world > 1:
                 everyone = [None] * world
-                dist.all_gather_object(everyone, handles, group=group)
-                for q, (h_recv, h_flags) in enumerate(everyone):
+                dist.all_gather_object(everyone, h.raw, group=group)
+                for q, h_recv in enumerate(everyone):
                     if q == rank:
                         continue
-                    for h, dst in ((h_recv, recv_ptrs), (h_flags, flag_ptrs)):
-                        ptr = C.c_void_p()
-                        _lib.check(lib.sphkv_xchg_open(h, C.byref(ptr)), "sphkv_xchg_open")
-                        self._opened.append(ptr.value)
-                        dst[q] = ptr.value
+                    ptr = C.c_void_p()
+                    _lib.check(lib.sphkv_xchg_open(h_recv, C.byref(ptr)), "sphkv_xchg_open")
+                    self._opened.append(ptr.value)
+                    recv_ptrs[q] = ptr.value
                 dist.barrier(group=group)  # every rank has opened every buffer before anyone decodes
         self.seq = torch.zeros(self.units, dtype=torch.int32, device=dev)
         self.recv_ptrs = torch.tensor(recv_ptrs, dtype=torch.int64, device=dev)
-        self.flag_ptrs = torch.tensor(flag_ptrs, dtype=torch.int64, device=dev)
 
     def check_shape(self, B: int, Hq: int, Hkv: int, dh: int) -> None:
         if (B, Hq, Hkv, dh) != (self.B, self.Hq, self.Hkv, self.dh):

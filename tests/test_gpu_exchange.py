@@ -2,9 +2,10 @@
 
 A second rank is stood in for by buffers on the same GPU that the test fills by hand, so no
 kernel ever waits for another launch: the rank under test stores its rows into "both ranks'"
-receive buffers, finds the other rank's flag already set and combines.  The bounded wait is
-exercised with a flag that nothing sets: the kernel must give up, raise the status bit, write
-zeros and return, and the context must stay usable.
+receive buffers, finds the other rank's words already there (each 64-bit word carries the step
+number beside its value) and combines.  The bounded wait is exercised with words that nothing
+writes: the kernel must give up, raise the status bit, write zeros and return, and the context
+must stay usable.
 """
 import pytest
 import torch
@@ -22,11 +23,9 @@ class HandMadeExchange(pkg.split_kv.ExchangeState):
 
     def __init__(self, rank, world, B, Hq, Hkv, dh, timeout_cycles=0):
         super().__init__(rank, world, B, Hq, Hkv, dh)
-        self.recv_all = [torch.zeros(self.recv_numel, device=DEV) for _ in range(world)]
-        self.flags_all = [torch.zeros(self.flags_numel, dtype=torch.int32, device=DEV) for _ in range(world)]
+        self.recv_all = [torch.zeros(self.recv_numel, dtype=torch.int64, device=DEV) for _ in range(world)]
         self.seq = torch.zeros(self.units, dtype=torch.int32, device=DEV)
         self.recv_ptrs = torch.tensor([t.data_ptr() for t in self.recv_all], dtype=torch.int64, device=DEV)
-        self.flag_ptrs = torch.tensor([t.data_ptr() for t in self.flags_all], dtype=torch.int64, device=DEV)
         self.timeout_cycles = timeout_cycles
 
     def check_shape(self, B, Hq, Hkv, dh):
@@ -36,9 +35,7 @@ class HandMadeExchange(pkg.split_kv.ExchangeState):
         """What rank `src_rank` would have stored into the running rank's memory in step `seq`."""
         mine = self.recv_all[self.rank]
         off = self.row_offset(seq, src_rank, 0)
-        mine[off:off + partial.numel()] = partial.reshape(-1)
-        fo = self.flag_offset(seq, src_rank, 0)
-        self.flags_all[self.rank][fo:fo + self.units] = seq
+        mine[off:off + partial.numel()] = self.pack(partial.reshape(-1), seq)
 
 
 def make_cache(B=2, Hq=8, Hkv=2, dh=128, ctx=900, seed=3):
@@ -74,14 +71,14 @@ def test_exchange_combines_with_prepublished_peer_rows_over_two_steps(world, ran
         # the same tiles, merged over ranks instead of over CTAs (tolerance of the shard-merge test)
         assert (got - want).abs().max().item() <= 2e-5 * want.abs().max().item() + 1e-6
         assert ex.seq.tolist() == [step] * ex.units
-        # the rank's own rows and flags went out to every rank's buffers
+        # the rank's own rows went out to every rank's buffers, every word stamped with the step
         own = torch.empty(B, Hq, dh + 2, device=DEV)
         pkg.decode_paged(q, shards[rank], rope, out_partial=own, want_out=False)
         for r in range(world):
             off = ex.row_offset(step, rank, 0)
-            assert torch.equal(ex.recv_all[r][off:off + own.numel()], own.reshape(-1))
-            fo = ex.flag_offset(step, rank, 0)
-            assert ex.flags_all[r][fo:fo + ex.units].tolist() == [step] * ex.units
+            vals, seqs = ex.unpack(ex.recv_all[r][off:off + own.numel()])
+            assert torch.equal(vals, own.reshape(-1))
+            assert (seqs == step).all()
 
 
 def test_exchange_wait_gives_up_and_reports_when_a_rank_never_publishes():
@@ -89,7 +86,7 @@ def test_exchange_wait_gives_up_and_reports_when_a_rank_never_publishes():
     B, Hq, dh = Q.shape
     shard = pkg.split_kv.shard_cache(cache, 0, 2)
     ex = HandMadeExchange(0, 2, B, Hq, cache.lists.Hkv, dh, timeout_cycles=200_000)  # ~0.1 ms
-    out = pkg.decode_paged(Q, shard, rope, exchange=ex)     # rank 1's flags are never set
+    out = pkg.decode_paged(Q, shard, rope, exchange=ex)     # rank 1's words never arrive
     torch.cuda.synchronize()
     assert int(shard.status.item()) & pkg._lib.ST_TIMEOUT
     assert (out == 0).all()

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), name
     assert declared == set(pkg._lib.SIGNATURES), declared ^ set(pkg._lib.SIGNATURES)
-    assert pkg._lib.load().sphkv_abi_version() == 3
+    assert pkg._lib.load().sphkv_abi_version() == 4
 
 
 def test_struct_sizes_match_header_layout():
