@@ -1079,7 +1079,6 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
   const int u = blockIdx.x;  // traversal index: hkv * B + b
   const int hkv = u / p.B, b = u - hkv * p.B;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __shared__ int s_c[2];
   __shared__ float s_M[8], s_L[8];
   __shared__ float s_w[8][kChunk];
   // The next kernel in the stream -- the next step's decode kernel -- may become resident now; it
@@ -1089,29 +1088,70 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
   const int32_t* pfx = a.pfx;
   const int64_t T = pfx[a.n_units];
   const int64_t ps = pfx[u], pe = pfx[u + 1];
-  if (threadIdx.x == 0) {
-    int c_lo = 0, c_hi = -1;
-    if (pe > ps && T > 0) {
-      c_lo = (int)((ps * a.n_ctas) / T);
-      if (c_lo >= a.n_ctas) c_lo = a.n_ctas - 1;
-      while (c_lo > 0 && cta_range_start(c_lo, a.n_ctas, T) > ps) --c_lo;
-      while (cta_range_start(c_lo + 1, a.n_ctas, T) <= ps) ++c_lo;
-      c_hi = (int)(((pe - 1) * a.n_ctas) / T);
-      if (c_hi >= a.n_ctas) c_hi = a.n_ctas - 1;
-      while (c_hi > c_lo && cta_range_start(c_hi, a.n_ctas, T) >= pe) --c_hi;
-      while (c_hi + 1 < a.n_ctas && cta_range_start(c_hi + 1, a.n_ctas, T) < pe) ++c_hi;
-    }
-    s_c[0] = c_lo;
-    s_c[1] = c_hi;
+  // the CTAs whose block ranges meet this unit's (every thread derives them: no barrier, no
+  // shared-memory round trip between the prefix loads and the row loads)
+  int c_lo = 0, c_hi = -1;
+  if (pe > ps && T > 0) {
+    c_lo = (int)((ps * a.n_ctas) / T);
+    if (c_lo >= a.n_ctas) c_lo = a.n_ctas - 1;
+    while (c_lo > 0 && cta_range_start(c_lo, a.n_ctas, T) > ps) --c_lo;
+    while (cta_range_start(c_lo + 1, a.n_ctas, T) <= ps) ++c_lo;
+    c_hi = (int)(((pe - 1) * a.n_ctas) / T);
+    if (c_hi >= a.n_ctas) c_hi = a.n_ctas - 1;
+    while (c_hi > c_lo && cta_range_start(c_hi, a.n_ctas, T) >= pe) --c_hi;
+    while (c_hi + 1 < a.n_ctas && cta_range_start(c_hi + 1, a.n_ctas, T) < pe) ++c_hi;
   }
-  __syncthreads();
-  const int c_lo = s_c[0], c_hi = s_c[1], nrows = c_hi - c_lo + 1;
+  const int nrows = c_hi - c_lo + 1;
+  auto row_exists = [&](int c) -> bool {
+    return cta_range_start(c, a.n_ctas, T) != cta_range_start(c + 1, a.n_ctas, T);
+  };
   auto row_m = [&](int n, int c) -> float {  // max of row (c, u) for head n; -inf if no such row
-    if (cta_range_start(c, a.n_ctas, T) == cta_range_start(c + 1, a.n_ctas, T)) return -INFINITY;
+    if (!row_exists(c)) return -INFINITY;
     return a.rows[((int64_t)(c + u) * 8 + n) * (DH + 2)];
   };
-  // pass 1: warp n -> global max and sum of head n
-  if (warp < a.grp) {
+  float o_acc[(8 * DH + 255) / 256];
+#pragma unroll
+  for (int q = 0; q < (8 * DH + 255) / 256; ++q) o_acc[q] = 0.f;
+  const bool few_rows = nrows <= 32;
+  if (few_rows) {
+    // At most one row per lane (the usual case: units >= CTAs / 32).  A warp covers 32 dimensions
+    // of one head: lane c fetches row c's (max, sum) while the accumulator loads of the first
+    // rows are already in flight, the warp reduces, and every lane then folds the rows of its
+    // dimension with the weights passed around by shuffles -- one memory latency instead of the
+    // four of the general path below, and the same arithmetic in the same order.
+#pragma unroll
+    for (int q = 0; q < (8 * DH + 255) / 256; ++q) {
+      const int i = threadIdx.x + q * 256;
+      const int n = i / DH, d = i - n * DH;
+      if (n >= a.grp) continue;  // warp-uniform: DH is a multiple of 32
+      const float* col = a.rows + ((int64_t)(c_lo + u) * 8 + n) * (DH + 2);
+      const bool mine = lane < nrows && row_exists(c_lo + lane);
+      const float mr = mine ? col[(int64_t)lane * 8 * (DH + 2)] : -INFINITY;
+      const float lr = mine ? col[(int64_t)lane * 8 * (DH + 2) + 1] : 0.f;
+      float M = mr;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+      const float w = (mine && M != -INFINITY) ? exp2f(mr - M) : 0.f;
+      float L = lr * w;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+      if (lane == 0 && d == 0) { s_M[n] = M; s_L[n] = L; }
+      float o = 0.f;
+      for (int ci = 0; ci < nrows; ci += 8) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = ci + k < nrows ? col[(int64_t)(ci + k) * 8 * (DH + 2) + 2 + d] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float wk = __shfl_sync(0xffffffffu, w, (ci + k) & 31);
+          o += (ci + k < nrows && wk != 0.f) ? wk * v[k] : 0.f;
+        }
+      }
+      o_acc[q] = o;
+    }
+    __syncthreads();
+  } else if (warp < a.grp) {
+    // pass 1: warp n -> global max and sum of head n
     float M = -INFINITY;
     for (int i = lane; i < nrows; i += 32) M = fmaxf(M, row_m(warp, c_lo + i));
 #pragma unroll
@@ -1127,7 +1167,7 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
     for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
     if (lane == 0) { s_M[warp] = M; s_L[warp] = L; }
   }
-  __syncthreads();
+  if (!few_rows) __syncthreads();
   // page-importance EMA (_omega_ema_eager, spherical_kv_pipeline.py:952-987) from the per-tile
   // (max, sum) the split-K kernel left in page_ml: per query head the block weights
   // exp(max(m - m_max, -60)) * l are normalised over the blocks, averaged over the heads of
@@ -1163,11 +1203,8 @@ __global__ void __launch_bounds__(256) merge_rows_kernel(const DecodeArgs a) {
     }
   }
   if (blockIdx.y != 0) return;  // only the first CTA of a unit writes the attention output
-  // pass 2: weights per chunk of rows, then threads over (head, dim)
-  float o_acc[(8 * DH + 255) / 256];
-#pragma unroll
-  for (int q = 0; q < (8 * DH + 255) / 256; ++q) o_acc[q] = 0.f;
-  for (int c0 = 0; c0 < nrows; c0 += kChunk) {
+  // pass 2 of the general path: weights per chunk of rows, then threads over (head, dim)
+  for (int c0 = 0; c0 < (few_rows ? 0 : nrows); c0 += kChunk) {
     const int nc = min(kChunk, nrows - c0);
     for (int i = threadIdx.x; i < a.grp * nc; i += blockDim.x) {
       const int n = i / nc, ci = i - n * nc;
