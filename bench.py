@@ -579,7 +579,11 @@ def splitkv_block(args, pkg, dev, rank, world):
     if world == 1:
         blk.update({"us_per_step": t1_us, "efficiency": 1.0, "exchange": "none (one GPU)"})
         return blk
-    ex = pkg.split_kv.PeerExchange(1, Hq, Hkv, dh, device=dev)
+    try:
+        ex = pkg.split_kv.PeerExchange(1, Hq, Hkv, dh, device=dev)
+    except Exception as exc:  # noqa: BLE001  (raised on every rank alike: see PeerExchange)
+        blk["error"] = f"peer exchange unavailable: {exc}"
+        return blk
 
     def split_step():
         for c, q, o in zip(shards, qs, out_split):
@@ -858,7 +862,12 @@ def main() -> None:
     del caches, graph
     torch.cuda.empty_cache()
     splitkv = None if args.no_side else splitkv_block(args, pkg, dev, rank, world)
-    encode_c4 = None if (args.no_side or rank != 0) else encode_c4_block(args, pkg, dev)
+    encode_c4 = None
+    if not args.no_side and rank == 0:
+        try:
+            encode_c4 = encode_c4_block(args, pkg, dev)
+        except Exception as exc:  # noqa: BLE001  (a side block must not cost the headline line)
+            encode_c4 = {"error": str(exc)}
     if rank == 0:
         if splitkv is not None:
             line["splitkv"] = splitkv

@@ -110,14 +110,26 @@ class PeerExchange(ExchangeState):
             if world > 1:
                 everyone = [None] * world
                 dist.all_gather_object(everyone, h.raw, group=group)
-                for q, h_recv in enumerate(everyone):
-                    if q == rank:
-                        continue
-                    ptr = C.c_void_p()
-                    _lib.check(lib.sphkv_xchg_open(h_recv, C.byref(ptr)), "sphkv_xchg_open")
-                    self._opened.append(ptr.value)
-                    recv_ptrs[q] = ptr.value
-                dist.barrier(group=group)  # every rank has opened every buffer before anyone decodes
+                failure = None
+                try:
+                    for q, h_recv in enumerate(everyone):
+                        if q == rank:
+                            continue
+                        ptr = C.c_void_p()
+                        _lib.check(lib.sphkv_xchg_open(h_recv, C.byref(ptr)), "sphkv_xchg_open")
+                        self._opened.append(ptr.value)
+                        recv_ptrs[q] = ptr.value
+                except _lib.SphKVError as exc:
+                    failure = f"rank {rank}: {exc}"
+                # every rank has opened every buffer before anyone decodes -- or every rank learns
+                # that one could not, and all of them give up together instead of one leaving the
+                # others in a collective
+                outcomes = [None] * world
+                dist.all_gather_object(outcomes, failure, group=group)
+                failed = [o for o in outcomes if o is not None]
+                if failed:
+                    self.close()
+                    raise _lib.SphKVError("peer exchange set-up failed: " + "; ".join(failed))
         self.seq = torch.zeros(self.units, dtype=torch.int32, device=dev)
         self.recv_ptrs = torch.tensor(recv_ptrs, dtype=torch.int64, device=dev)
 
