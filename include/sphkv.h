@@ -206,11 +206,17 @@ typedef struct sphkv_decode_params {
 #define SPHKV_ST_BAD_POSITION 1 /* a key position was outside [0, max_pos)            */
 #define SPHKV_ST_BAD_BLOCK 2    /* a block-table entry was >= n_pages                 */
 #define SPHKV_ST_BAD_SLOT 4     /* a bits-table entry was outside [0, n_slots)        */
-#define SPHKV_ST_TIMEOUT 8      /* an asynchronous copy did not complete within the
-                                   kernel's bounded wait; the output is not valid     */
+#define SPHKV_ST_TIMEOUT 8      /* an asynchronous copy, or another rank's part of a split-KV
+                                   exchange, did not arrive within the kernel's bounded
+                                   wait; the output is not valid                      */
 #define SPHKV_ST_INTERNAL 16    /* the kernel found its shared memory misaligned      */
 
 int64_t sphkv_decode_scratch_bytes(int32_t B, int32_t Hkv, int32_t dh, int32_t n_ctas);
+/* Two launches on `stream`: the split-K decode kernel and the merge kernel.  The decode kernel is
+ * launched with programmatic stream serialization: its CTAs may become resident while the kernel
+ * before it in the stream is still running, but it reads and writes no global memory before that
+ * kernel has completed, so stream order is what the caller observes (and what a CUDA graph
+ * captured from the stream replays). */
 int sphkv_decode_paged(const sphkv_decode_params* p, void* stream);
 
 /* Has no counterpart in the reference.  Same operation, arguments and results as
