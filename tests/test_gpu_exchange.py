@@ -51,9 +51,11 @@ def make_cache(B=2, Hq=8, Hkv=2, dh=128, ctx=900, seed=3):
     return cache, rope, Q.to(DEV)
 
 
-@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (3, 1)])
-def test_exchange_combines_with_prepublished_peer_rows_over_two_steps(world, rank):
-    cache, rope, Q = make_cache()
+@pytest.mark.parametrize("world,rank,shape", [(2, 0, {}), (2, 1, {}), (3, 1, {}),
+                                              (4, 2, dict(B=3, Hq=4, Hkv=2, dh=64, ctx=500)),
+                                              (8, 7, dict(B=1, Hq=8, Hkv=1, dh=128, ctx=2100))])
+def test_exchange_combines_with_prepublished_peer_rows_over_two_steps(world, rank, shape):
+    cache, rope, Q = make_cache(**shape)
     B, Hq, dh = Q.shape
     Hkv = cache.lists.Hkv
     shards = [pkg.split_kv.shard_cache(cache, r, world) for r in range(world)]
