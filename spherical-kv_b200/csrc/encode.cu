@@ -25,6 +25,7 @@ struct EncodeArgs {
   sphkv_encode_params p;
   int bundles_per_cta;
   int warp_smem_bytes;  // page assembly: shared memory of one warp
+  int search_chunk;     // search launch: consecutive bundles a CTA takes at a time (1 .. 8)
 };
 
 constexpr int kEncThreads = 256;
@@ -96,12 +97,64 @@ __device__ __forceinline__ uint4 load_v_chunk(const sphkv_encode_params& p, bool
 
 constexpr int kMaxBundlesPerCta = 8;  // consecutive bundles one CTA walks (they mostly share a codebook)
 
-// PHASE 0: everything in one kernel (no scratch needed).  PHASE 1: radius + nearest-centroid
-// search only, results to the scratch arrays r[(page*N + slot) * (dh/16) + group] (f32) and
-// theta[...] (u8); assemble_pages_kernel then builds the pages and the V pages from those arrays.
-// Splitting lets the FMA-bound search run without the barriers and small dependent loads of the
-// page bookkeeping.
-template <int GS, int PHASE>
+// Squared norm and nearest centroid of four tokens' GS-dim group vectors: the fixed fma chains that
+// define the encoder bit for bit (d = 0 .. GS-1 from 0; first maximum wins).  Every centroid row
+// read from shared memory (`cbg`, [C][GS]) feeds four dot products.
+template <int GS>
+__device__ __forceinline__ void search_four_tokens(const float (&k)[4][GS], const float* __restrict__ cbg, int C,
+                                                   float (&nsq)[4], int (&code)[4]) {
+#pragma unroll
+  for (int h = 0; h < 4; ++h) nsq[h] = 0.f;
+#pragma unroll
+  for (int d = 0; d < GS; ++d)
+#pragma unroll
+    for (int h = 0; h < 4; ++h) nsq[h] = __fmaf_rn(k[h][d], k[h][d], nsq[h]);
+  float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int h = 0; h < 4; ++h) code[h] = 0;
+  SPHKV_UNROLL_SEARCH
+  for (int c = 0; c < C; ++c) {
+    const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < GS / 4; ++i) {
+      const float4 v = row[i];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        sacc[h] = __fmaf_rn(k[h][4 * i], v.x, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][4 * i + 1], v.y, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][4 * i + 2], v.z, sacc[h]);
+        sacc[h] = __fmaf_rn(k[h][4 * i + 3], v.w, sacc[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+      if (sacc[h] > best[h]) { best[h] = sacc[h]; code[h] = c; }
+  }
+}
+
+// The codebook of one (KV head, tier slot), [G][C][GS] packed, global -> shared memory.
+template <int GS>
+__device__ __forceinline__ void stage_slot_codebook(const sphkv_encode_params& p, int head, int slot, float* cb_s) {
+  const int bits = p.tiers.bits[slot], G = p.dh / GS;
+  const float4* src = reinterpret_cast<const float4*>(
+      p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max * p.tiers.g_max);
+  float4* dst = reinterpret_cast<float4*>(cb_s);
+  constexpr int Q4 = GS / 4;
+  const int total = (G << bits) * Q4;
+  const int row_stride4 = p.tiers.g_max >> 2;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int q4 = i % Q4, row = i / Q4;
+    const int c = row & ((1 << bits) - 1), gam = row >> bits;
+    dst[i] = __ldg(src + ((int64_t)gam * p.tiers.C_max + c) * row_stride4 + q4);
+  }
+}
+
+// Everything in one kernel (the route without scratch): search, page images and V pages per bundle.
+// With scratch the work is split instead: search_bundles_kernel writes radius + centroid index per
+// (page slot, group) and assemble_pages_kernel builds the pages, so the FMA-bound search runs without
+// the barriers and small dependent loads of the page bookkeeping.
+template <int GS>
 __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const EncodeArgs a) {
   const sphkv_encode_params& p = a.p;
   extern __shared__ __align__(16) uint8_t smem[];
@@ -113,9 +166,6 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
   const int n_shift = 31 - __clz(N);  // page_size is a power of two
   const int rb = p.radius_fmt == SPHKV_RADIUS_F16 ? 2 : 1;
   const int C_cap = p.tiers.C_max;
-  const int GST = dh >> 4;  // group stride of the scratch arrays
-  float* scr_r = reinterpret_cast<float*>(p.scratch);
-  uint8_t* scr_t = reinterpret_cast<uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
 
   float* cb_s = reinterpret_cast<float*>(smem);                       // [G][C][GS]
   float* r_s = cb_s + G * C_cap * GS;                                  // [TB][G]
@@ -162,18 +212,7 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
 
     // ---- codebook of (head, slot) -> shared memory, 128-bit copies ---------------------------
     if (head * p.tiers.n_slots + slot != loaded_key) {
-      const float4* src = reinterpret_cast<const float4*>(
-          p.codebooks + ((int64_t)(head * p.tiers.n_slots + slot) * p.tiers.G_max) * p.tiers.C_max *
-                            p.tiers.g_max);
-      float4* dst = reinterpret_cast<float4*>(cb_s);
-      constexpr int Q4 = GS / 4;
-      const int total = (G << bits) * Q4;
-      const int row_stride4 = p.tiers.g_max >> 2;
-      for (int i = threadIdx.x; i < total; i += blockDim.x) {
-        const int q4 = i % Q4, row = i / Q4;
-        const int c = row & (C - 1), gam = row >> bits;
-        dst[i] = __ldg(src + ((int64_t)gam * p.tiers.C_max + c) * row_stride4 + q4);
-      }
+      stage_slot_codebook<GS>(p, head, slot, cb_s);
       loaded_key = head * p.tiers.n_slots + slot;
       __syncthreads();
     }
@@ -199,51 +238,17 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
           for (int i = 0; i < GS; ++i) k[h][i] = 0.f;
         }
       }
-      float nsq[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int d = 0; d < GS; ++d)
-#pragma unroll
-        for (int h = 0; h < 4; ++h) nsq[h] = __fmaf_rn(k[h][d], k[h][d], nsq[h]);
-      float best[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      int code[4] = {0, 0, 0, 0};
-      SPHKV_UNROLL_SEARCH
-      for (int c = 0; c < C; ++c) {
-        const float4* row = reinterpret_cast<const float4*>(cbg + c * GS);
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < GS / 4; ++i) {
-          const float4 v = row[i];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            sacc[h] = __fmaf_rn(k[h][4 * i], v.x, sacc[h]);
-            sacc[h] = __fmaf_rn(k[h][4 * i + 1], v.y, sacc[h]);
-            sacc[h] = __fmaf_rn(k[h][4 * i + 2], v.z, sacc[h]);
-            sacc[h] = __fmaf_rn(k[h][4 * i + 3], v.w, sacc[h]);
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < 4; ++h)
-          if (sacc[h] > best[h]) { best[h] = sacc[h]; code[h] = c; }
-      }
+      float nsq[4];
+      int code[4];
+      search_four_tokens<GS>(k, cbg, C, nsq, code);
 #pragma unroll
       for (int h = 0; h < 4; ++h) {
         const int ts = lane + 32 * h;
         const float rv = have[h] ? __fsqrt_rn(nsq[h]) : 0.f;
-        if (PHASE == 1) {
-          const int q = ts >> n_shift, tin = ts & (N - 1);
-          const int page = page_s[q];
-          if (page >= 0) {
-            const int64_t si = ((int64_t)page * N + tin) * GST + warp;
-            scr_r[si] = rv;
-            scr_t[si] = (uint8_t)code[h];
-          }
-        } else {
-          r_s[ts * G + warp] = rv;
-          th_s[ts * G + warp] = (uint8_t)code[h];
-        }
+        r_s[ts * G + warp] = rv;
+        th_s[ts * G + warp] = (uint8_t)code[h];
       }
     }
-    if (PHASE == 1) continue;  // the assembly launch takes it from here
     __syncthreads();
 
     // ---- per-page, per-group scale = max radius over the page's tokens ----------------------
@@ -388,6 +393,113 @@ __global__ void __launch_bounds__(kEncThreads) encode_bundle_kernel(const Encode
 #pragma unroll
         for (int u = 0; u < kInFlight; ++u)
           if (dst[u] >= 0) reinterpret_cast<uint4*>(p.v_pool)[dst[u]] = o[u];
+      }
+    }
+  }
+}
+
+// ---- search only (the split route) ---------------------------------------------------------
+// Radius and nearest centroid of every token slot of every bundle, written to the scratch arrays
+// r[(page * N + slot) * (dh / 16) + group] (f32) and theta[...] (u8).  Persistent: CTA c of n takes
+// the chunks c, c + n, c + 2n, ... of `search_chunk` consecutive bundles (1 .. 8: consecutive bundles
+// mostly share a codebook, and every CTA should still get several chunks; striding the chunks
+// spreads the tiers, whose bundles differ fourfold in work, evenly over the CTAs); warp = group,
+// lane = four token slots.  The only barrier is the codebook change between (head, tier) keys;
+// otherwise a warp walks its bundles alone, and while it searches one bundle the page ids and
+// source rows of the next are already loaded and its key rows are on their way to L2.
+template <int GS>
+__global__ void __launch_bounds__(kEncThreads, GS == 16 ? 2 : 1) search_bundles_kernel(const EncodeArgs a) {
+  const sphkv_encode_params& p = a.p;
+  extern __shared__ __align__(16) uint8_t smem[];
+  float* cb_s = reinterpret_cast<float*>(smem);  // [G][C][GS] of the current (head, tier slot)
+  const int N = p.page_size, dh = p.dh;
+  const int ppb = 128 / N, n_shift = 31 - __clz(N);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = dh / GS, GST = dh >> 4;
+  const int esize = p.k_dtype == SPHKV_F32 ? 4 : 2;
+  const int chunk_len = a.search_chunk;
+  float* scr_r = reinterpret_cast<float*>(p.scratch);
+  uint8_t* scr_t = reinterpret_cast<uint8_t*>(p.scratch) + (int64_t)p.n_pages * N * GST * 4;
+  // page and source row of this lane's four token slots of bundle bi
+  auto lookup = [&](int64_t bi, int (&pg)[4], int (&row)[4]) {
+    const int32_t* bundle = p.bundles + 8 * bi;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const int ts = lane + 32 * h;
+      pg[h] = bundle[ts >> n_shift];
+      row[h] = pg[h] >= 0 ? p.src_index[(int64_t)pg[h] * N + (ts & (N - 1))] : -1;
+    }
+  };
+  int loaded_key = -1;
+  for (int64_t chunk = blockIdx.x; chunk * chunk_len < p.n_bundles; chunk += gridDim.x) {
+    // lane q < chunk_len looks at bundle q of the chunk: which (head, tier slot), and is it of this
+    // launch's group size?  One pair of dependent loads per chunk; bundles of the other group size
+    // (the other launch takes them) cost nothing more.
+    int my_head = -1, my_slot = 0;
+    if (lane < chunk_len && chunk * chunk_len + lane < p.n_bundles) {
+      const int32_t* bundle = p.bundles + 8 * (chunk * chunk_len + lane);
+      int first = -1;
+      for (int q = 0; q < ppb; ++q) {
+        const int pq = bundle[q];
+        if (first < 0 && pq >= 0) first = pq;
+      }
+      if (first >= 0) {
+        my_head = p.page_head[first];
+        my_slot = p.page_slot[first];
+      }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, my_head >= 0 && p.tiers.g[my_slot] == GS);  // same in every warp
+    int pg_n[4], row_n[4];
+    if (todo) lookup(chunk * chunk_len + (__ffs(todo) - 1), pg_n, row_n);
+    while (todo) {
+      const int q = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const int head = __shfl_sync(0xffffffffu, my_head, q), slot = __shfl_sync(0xffffffffu, my_slot, q);
+      int pg[4], row[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) { pg[h] = pg_n[h]; row[h] = row_n[h]; }
+      int head_n = -1;
+      if (todo) {  // the next bundle of the chunk: its rows load while this one is searched
+        const int qn = __ffs(todo) - 1;
+        head_n = __shfl_sync(0xffffffffu, my_head, qn);
+        lookup(chunk * chunk_len + qn, pg_n, row_n);
+      }
+      if (head * p.tiers.n_slots + slot != loaded_key) {
+        __syncthreads();  // every warp is done with the previous codebook
+        stage_slot_codebook<GS>(p, head, slot, cb_s);
+        loaded_key = head * p.tiers.n_slots + slot;
+        __syncthreads();
+      }
+      if (warp >= G) continue;
+      if (head_n >= 0) {
+#pragma unroll
+        for (int h = 0; h < 4; ++h)
+          if (row_n[h] >= 0)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(
+                reinterpret_cast<const char*>(p.k_src) +
+                ((int64_t)row_n[h] * p.k_row_stride + (int64_t)head_n * p.k_head_stride + warp * GS) * esize));
+      }
+      const int bits = p.tiers.bits[slot];
+      float k[4][GS];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (row[h] >= 0) {
+          load_group<GS>(p.k_src, p.k_dtype,
+                         (int64_t)row[h] * p.k_row_stride + (int64_t)head * p.k_head_stride + warp * GS, k[h]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < GS; ++i) k[h][i] = 0.f;
+        }
+      }
+      float nsq[4];
+      int code[4];
+      search_four_tokens<GS>(k, cb_s + (warp << bits) * GS, 1 << bits, nsq, code);
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        if (pg[h] < 0) continue;
+        const int64_t si = ((int64_t)pg[h] * N + ((lane + 32 * h) & (N - 1))) * GST + warp;
+        scr_r[si] = row[h] >= 0 ? __fsqrt_rn(nsq[h]) : 0.f;
+        scr_t[si] = (uint8_t)code[h];
       }
     }
   }
@@ -774,13 +886,21 @@ using namespace sphkv;
 
 template <int GS>
 static int launch_encode(const EncodeArgs& a, bool split, int smem_bytes, cudaStream_t st) {
-  const int grid = (a.p.n_bundles + a.bundles_per_cta - 1) / a.bundles_per_cta;
   if (split) {
-    encode_bundle_kernel<GS, 1><<<grid, kEncThreads, smem_bytes, st>>>(a);
-    return check_launch("encode_bundle_kernel<search>");
+    // persistent: as many CTAs as are resident at once, each striding over chunks of bundles
+    static SmemOptIn opt_in;
+    const int cb_bytes = a.p.dh * a.p.tiers.C_max * 4;
+    if (int rc = ensure_dynamic_smem(opt_in, (const void*)search_bundles_kernel<GS>, cb_bytes, "encode search")) return rc;
+    const int resident = sm_count_current_device() * (GS == 16 ? 2 : 1);
+    EncodeArgs b = a;
+    b.search_chunk = std::max(1, std::min(8, a.p.n_bundles / (resident * 4)));  // >= 4 chunks per CTA, <= 8 bundles each
+    const int grid = std::max(1, std::min((a.p.n_bundles + b.search_chunk - 1) / b.search_chunk, resident));
+    search_bundles_kernel<GS><<<grid, kEncThreads, cb_bytes, st>>>(b);
+    return check_launch("search_bundles_kernel");
   }
-  encode_bundle_kernel<GS, 0><<<grid, kEncThreads, smem_bytes, st>>>(a);
-  return check_launch("encode_bundle_kernel<fused>");
+  const int grid = (a.p.n_bundles + a.bundles_per_cta - 1) / a.bundles_per_cta;
+  encode_bundle_kernel<GS><<<grid, kEncThreads, smem_bytes, st>>>(a);
+  return check_launch("encode_bundle_kernel");
 }
 
 // One warp per page of the bundle list, every tier slot in the same launch.
@@ -861,10 +981,9 @@ static int encode_impl(const sphkv_encode_params* pp, void* stream, bool from_co
                      ((uintptr_t)p.scratch & 15) == 0;
   if (from_codes) return launch_assemble(a, true, st);
   {
-    static SmemOptIn opt_in[4];
-    const void* kernels[4] = {(const void*)encode_bundle_kernel<16, 0>, (const void*)encode_bundle_kernel<16, 1>,
-                              (const void*)encode_bundle_kernel<32, 0>, (const void*)encode_bundle_kernel<32, 1>};
-    for (int i = 0; i < 4; ++i)
+    static SmemOptIn opt_in[2];
+    const void* kernels[2] = {(const void*)encode_bundle_kernel<16>, (const void*)encode_bundle_kernel<32>};
+    for (int i = 0; i < 2; ++i)
       if (int rc = ensure_dynamic_smem(opt_in[i], kernels[i], smem_bytes, "encode")) return rc;
   }
   // One search launch per group size present; each skips the bundles of the other size.
