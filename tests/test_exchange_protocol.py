@@ -32,7 +32,10 @@ def _step(st, recv_all, seq, my_rows):
     t0 = time.monotonic()
     mine = recv_all[st.rank]
     while True:
-        got = [st.unpack(mine[st.row_offset(seq, q, 0):st.row_offset(seq, q, 0) + st.rows * w]) for q in range(st.world)]
+        # one read of every word (a private copy), as the kernel's single 64-bit load: value and step
+        # number must come from the same moment
+        got = [st.unpack(mine[st.row_offset(seq, q, 0):st.row_offset(seq, q, 0) + st.rows * w].clone())
+               for q in range(st.world)]
         if all(st.arrived(int(s), seq) for _, seqs in got for s in seqs.tolist()):
             break
         if time.monotonic() - t0 > TIMEOUT_S:
